@@ -1,0 +1,30 @@
+// Version, error strings and per-thread launch-error bookkeeping of the C ABI.
+#include "spk_common.cuh"
+
+namespace {
+thread_local int g_last_cuda_error = 0;
+}
+
+int spk_set_cuda_error(cudaError_t err) {
+    g_last_cuda_error = static_cast<int>(err);
+    return SPK_ERR_CUDA;
+}
+
+extern "C" int spk_version(void) { return (0 << 16) | (1 << 8) | 0; }
+
+extern "C" int spk_last_cuda_error(void) { return g_last_cuda_error; }
+
+extern "C" const char* spk_error_string(int code) {
+    switch (code) {
+        case SPK_OK: return "ok";
+        case SPK_ERR_BAD_DTYPE: return "unsupported element type";
+        case SPK_ERR_BAD_SHAPE: return "invalid shape or size argument";
+        case SPK_ERR_BAD_STRIDE: return "invalid stride argument";
+        case SPK_ERR_NULL_POINTER: return "required pointer is null";
+        case SPK_ERR_WORKSPACE_TOO_SMALL: return "workspace missing or too small";
+        case SPK_ERR_UNSUPPORTED: return "configuration not supported";
+        case SPK_ERR_TOO_LARGE: return "problem exceeds a launch or capacity limit";
+        case SPK_ERR_CUDA: return "CUDA launch failed (see spk_last_cuda_error)";
+        default: return "unknown error code";
+    }
+}

@@ -1,0 +1,67 @@
+"""The C-ABI library: it builds, loads and exports exactly what include/spikeinfer_b200.h declares.
+Host-side argument validation is exercised too; none of these calls launches a kernel."""
+from __future__ import annotations
+
+import ctypes
+import re
+from pathlib import Path
+
+from spikeinfer_b200 import _lib
+
+HEADER = Path(__file__).resolve().parent.parent / "include" / "spikeinfer_b200.h"
+
+
+def declared_symbols() -> list[str]:
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return re.findall(r"^\s*(?:const\s+char\s*\*|int64_t|int)\s+(spk_\w+)\s*\(", text, flags=re.M)
+
+
+def test_header_and_binding_agree():
+    names = declared_symbols()
+    assert len(names) == len(set(names)) and len(names) >= 15
+    assert set(names) == set(_lib.SIGNATURES)
+
+
+def test_library_exports_every_declared_symbol(lib):
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} is declared but not exported"
+
+
+def test_version_and_error_strings(lib):
+    assert lib.spk_version() == (0 << 16) | (1 << 8) | 0
+    assert lib.spk_error_string(0) == b"ok"
+    assert b"workspace" in lib.spk_error_string(-5)
+    assert b"unknown" in lib.spk_error_string(-12345)
+    assert lib.spk_last_cuda_error() == 0
+
+
+def test_site_struct_layout():
+    # 3 pointers/ints block + strides: must match `spk_lif_site` (all members 8-byte aligned)
+    assert ctypes.sizeof(_lib.LifSite) == 8 + 4 + 4 + 8 + 24 + 32 + 8 + 24 + 8 + 8 + 8 + 4 + 4 + 24
+
+
+def test_host_side_argument_checks(lib):
+    one = _lib.i64_array([1])
+    assert lib.spk_pack(None, _lib.F32, 1, one, one, 0, None, None) == -2       # no channels
+    assert lib.spk_pack(None, 99, 1, one, one, 8, None, None) == -4             # null before dtype
+    assert lib.spk_pack(1, 99, 1, one, one, 8, 1, None) == -1                   # bad dtype
+    assert lib.spk_pack(None, _lib.F32, 7, one, one, 8, None, None) == -2       # too many dims
+    assert lib.spk_unpack(None, 0, 8, None, _lib.F32, None) == 0                # empty is fine
+    assert lib.spk_lif(None, _lib.F32, 4, 0, 1, one, one, 8, None, None, None, None, _lib.F32, None, 7, None) == -6
+    assert lib.spk_lif_pack_scatter(None, 1, 4, 1, 0, None, None) == -4
+    # attention: head_dim must be a multiple of 32 up to 128, block_size a power of two
+    args = lambda hd, bs: (1, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 1, 1, _lib.F32, 0, 0, 0,
+                           4, 2, 14, 2, hd, bs, 4, 8, 0.125, None, 0, None, None)
+    assert lib.spk_attn_decode(*args(48, 16)) == -6
+    assert lib.spk_attn_decode(*args(64, 12)) == -6
+    assert lib.spk_attn_decode(*args(256, 16)) == -6
+    # split-KV plan: a short table needs no workspace, BASELINE config 2 (64 x 4096 keys) does
+    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 1) == 0
+    ws = lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 256)
+    assert ws == 64 * 4 * 2 * 8 * 7 * 65 * 4
+    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 48, 16, 256) == 0
+    # workspace required but missing -> rejected on the host, nothing launched
+    big = (1, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 1, 1, _lib.F32, 0, 0, 0,
+           4, 64, 14, 2, 64, 16, 256, 8, 0.125, None, 0, None, None)
+    assert lib.spk_attn_decode(*big) == -5
+    assert lib.spk_meta_advance(1, 1, 1, 1, 1, 1, 1, 1, None, 2048, 4, 0, 16, None, None) == -2

@@ -1,0 +1,78 @@
+"""Host-side behaviour of the operator wrappers that needs no GPU: shapes, errors, and that a CPU
+tensor is refused loudly (there is no CPU path in the product)."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from spikeinfer_b200 import _lib, kernels
+from spikeinfer_b200.kernels.packing import _leading_dims
+
+
+@pytest.mark.parametrize("channels", [1, 31, 32, 33, 63, 64, 128, 4864])
+def test_packed_width(channels):
+    assert kernels.packed_width(channels) == (channels + 31) // 32
+
+
+def test_packed_bytes_per_token():
+    assert kernels.packed_bytes_per_token(24, 4, 2, 64) == 3072
+    assert kernels.BITS_PER_WORD == 32
+
+
+def test_leading_dims_merge_and_drop():
+    x = torch.empty(4, 1, 14, 8, 64)
+    assert _leading_dims(x) == ([4 * 14 * 8], [64])
+    y = x.permute(0, 1, 3, 2, 4)  # [4,1,8,14,64], strided
+    assert _leading_dims(y) == ([4, 8, 14], [14 * 8 * 64, 64, 8 * 64])
+    assert _leading_dims(y, first=1) == ([8, 14], [64, 8 * 64])
+
+
+def test_cpu_tensors_are_refused(lib):
+    x = torch.ones(2, 64)
+    with pytest.raises(_lib.SpkError, match="no CPU path"):
+        kernels.pack_spikes(x)
+    with pytest.raises(_lib.SpkError, match="no CPU path"):
+        kernels.unpack_spikes(torch.zeros(2, 2, dtype=torch.int32), 64)
+    with pytest.raises(_lib.SpkError, match="no CPU path"):
+        kernels.lif_multistep(torch.zeros(4, 2, 64), torch.ones(64), torch.ones(64))
+    q = torch.zeros(4, 1, 14, 2, dtype=torch.int32)
+    c = torch.zeros(4, 2, 64, 2, dtype=torch.int32)
+    with pytest.raises(_lib.SpkError, match="no CPU path"):
+        kernels.paged_spike_attn_decode(q, c, c, torch.zeros(1, 4, dtype=torch.int32),
+                                        torch.ones(1, dtype=torch.int32), 64, 16, 14, 2)
+
+
+def test_reference_error_behaviour():
+    q = torch.zeros(4, 1, 14, 2, dtype=torch.int32)
+    c = torch.zeros(4, 2, 64, 2, dtype=torch.int32)
+    t = torch.zeros(1, 4, dtype=torch.int32)
+    n = torch.ones(1, dtype=torch.int32)
+    with pytest.raises(ValueError, match="q has 2 words, expected 4"):
+        kernels.paged_spike_attn_decode(q, c, c, t, n, 128, 16, 14, 2)
+    with pytest.raises(ValueError, match="q has 14 heads, expected 7"):
+        kernels.paged_spike_attn_decode(q, c, c, t, n, 64, 16, 7, 1)
+    with pytest.raises(ValueError, match="expected 4 words"):
+        kernels.unpack_spikes(torch.zeros(1, 2, dtype=torch.int32), 128)
+    with pytest.raises(AssertionError):
+        kernels.lif_multistep(torch.zeros(4), torch.ones(1), torch.ones(1))
+    with pytest.raises(AssertionError, match="beta/threshold must match"):
+        kernels.lif_multistep(torch.zeros(4, 2, 64), torch.ones(63), torch.ones(64))
+
+
+def test_validate_thresholds():
+    class Lif(torch.nn.Module):
+        def __init__(self, th):
+            super().__init__()
+            self.threshold = torch.nn.Parameter(torch.tensor(th))
+            self.beta = torch.nn.Parameter(torch.tensor([0.9] * len(th)))
+
+    class Site(torch.nn.Module):
+        def __init__(self, th):
+            super().__init__()
+            self.lif = Lif(th)
+
+    good = torch.nn.Sequential(Site([0.5, 1.0]), Site([0.1, 0.2]))
+    assert kernels.validate_thresholds(good) is True
+    bad = torch.nn.Sequential(Site([0.5, 1.0]), Site([0.0, 0.2]))
+    with pytest.raises(ValueError, match="threshold > 0"):
+        kernels.validate_thresholds(bad)
