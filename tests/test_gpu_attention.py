@@ -1,0 +1,198 @@
+"""GPU parity: paged popcount decode attention against the CPU oracle and the golden fixtures.
+
+Scores are compared exactly (integers); attention outputs to the reference's own bar for its
+kernel, 1e-5 of the largest magnitude in fp32 (tests/test_spike_attention.py:28,74-78), and to 1e-3
+for bf16 output.  Isolation and padding-tail checks are bit-exact, as in the reference.
+"""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import cases
+from conftest import to_dev
+from oracle import torch_oracle as orc
+from spikeinfer_b200 import _lib, kernels
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-5  # fp32 output, max-norm relative
+REL_TOL_BF16 = 1e-3  # bf16 output vs the oracle rounded to bf16, plus one bf16 ulp of rounding slack
+
+
+def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    scale = want.abs().max().clamp(min=1e-6)
+    return ((got.float() - want.float()).abs().max() / scale).item()
+
+
+def run(case, dev, **kw):
+    return kernels.paged_spike_attn_decode(**to_dev(case, dev), **kw)
+
+
+@pytest.mark.parametrize("name", list(cases.ATTENTION_CASES))
+def test_matches_oracle_and_golden(name, dev, golden):
+    case = cases.attention_case(**cases.ATTENTION_CASES[name])
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    got = run(case, dev, status=status).cpu()
+    assert torch.isfinite(got).all()
+    want = orc.paged_spike_attn_decode(**case)
+    assert rel_err(got, want) < REL_TOL, f"vs oracle: {rel_err(got, want):.2e}"
+    assert rel_err(got, golden("attention")[name]["out_ref"]) < REL_TOL
+    assert status.item() == 0
+
+
+@pytest.mark.parametrize("block_size", [1, 2, 8, 16, 32, 64, 128])
+def test_block_sizes(block_size, dev):
+    case = cases.attention_case(seq_lens=[1, 5, 40, 97, 130], block_size=block_size, seed=block_size)
+    assert rel_err(run(case, dev).cpu(), orc.paged_spike_attn_decode(**case)) < REL_TOL
+
+
+def test_scores_are_exact(dev):
+    for name in ("ragged", "d128_gqa7", "d96", "long_split"):
+        case = cases.attention_case(**cases.ATTENTION_CASES[name])
+        keys = ("q_packed", "k_cache", "block_tables", "seq_lens", "head_dim", "block_size", "num_q_heads", "num_kv_heads")
+        want = orc.qk_scores(**{k: case[k] for k in keys})
+        got = kernels.qk_scores(**to_dev({k: case[k] for k in keys}, dev))
+        assert torch.equal(got.cpu(), want), name
+
+
+def test_all_zero_query_gives_the_mean_of_the_values(dev):
+    case = cases.attention_case(seq_lens=[40, 17, 5], block_size=32)
+    case["q_packed"] = torch.zeros_like(case["q_packed"])
+    got = run(case, dev).cpu()
+    assert torch.isfinite(got).all()
+    assert rel_err(got, orc.paged_spike_attn_decode(**case)) < REL_TOL
+    v = orc.gather_kv_unpacked(case["v_cache"], case["block_tables"][1], 17, 64, 32)  # [T, Hkv, 17, D]
+    torch.testing.assert_close(got[:, 1, 0], v[:, 0].mean(dim=1), rtol=1e-5, atol=1e-6)
+
+
+def test_all_ones_query_and_keys(dev):
+    """Largest possible scores (64) everywhere: the fixed softmax bound must not overflow or lose weight."""
+    case = cases.attention_case(seq_lens=[33, 2], head_dim=128, num_q_heads=7, num_kv_heads=1)
+    case["q_packed"] = torch.full_like(case["q_packed"], -1)
+    got = run(case, dev).cpu()
+    assert rel_err(got, orc.paged_spike_attn_decode(**case)) < REL_TOL
+    case["k_cache"] = torch.full_like(case["k_cache"], -1)
+    got = run(case, dev).cpu()
+    assert rel_err(got, orc.paged_spike_attn_decode(**case)) < REL_TOL
+
+
+def test_only_owned_blocks_and_valid_positions_are_read(dev):
+    case = cases.attention_case(seq_lens=[9, 25, 41, 3, 600], max_blocks=64)
+    d = to_dev(case, dev)
+    before = kernels.paged_spike_attn_decode(**d).clone()
+    bs = case["block_size"]
+    owned = set()
+    for i, length in enumerate(case["seq_lens"].tolist()):
+        owned.update(case["block_tables"][i, : (length + bs - 1) // bs].tolist())
+    for blk in range(case["k_cache"].shape[2] // bs):
+        if blk not in owned:
+            d["k_cache"][:, :, blk * bs:(blk + 1) * bs] = -1
+            d["v_cache"][:, :, blk * bs:(blk + 1) * bs] = -1
+    for i, length in enumerate(case["seq_lens"].tolist()):
+        if length % bs:
+            last = int(case["block_tables"][i, (length - 1) // bs])
+            d["k_cache"][:, :, last * bs + length % bs:(last + 1) * bs] = -1
+            d["v_cache"][:, :, last * bs + length % bs:(last + 1) * bs] = -1
+    after = kernels.paged_spike_attn_decode(**d)
+    assert torch.equal(before, after), "attention read outside the sequence's blocks or past seq_len"
+
+
+def test_out_argument_strided_view_and_dtypes(dev):
+    """The engine passes out=buf[:, :n_dec] (attention.py:157): a strided view in the model dtype."""
+    case = cases.attention_case(seq_lens=[1, 5, 40, 97])
+    want = orc.paged_spike_attn_decode(**case)
+    for dtype, tol in ((torch.float32, REL_TOL), (torch.bfloat16, None), (torch.float16, 1e-3)):
+        buf = torch.full((4, 9, 14, 64), 7.0, dtype=dtype, device=dev)
+        ret = run(case, dev, out=buf[:, :4])
+        assert ret.data_ptr() == buf.data_ptr()
+        assert (buf[:, 4:] == 7.0).all(), "wrote past the requested rows"
+        got = buf[:, :4].cpu()
+        if dtype == torch.bfloat16:
+            # within 1e-3 of the fp32 result before rounding => at most one bf16 step from the rounded oracle
+            w16 = want.to(torch.bfloat16).float()
+            ulp = torch.maximum(w16.abs() * 2.0 ** -7, torch.tensor(1e-30))
+            assert ((got.float() - w16).abs() <= ulp).all()
+            assert rel_err(got, want) < 2.0 ** -8 + REL_TOL_BF16
+        else:
+            assert rel_err(got, want) < tol
+    assert run(case, dev, dtype=torch.bfloat16).dtype == torch.bfloat16
+
+
+def test_strided_pool_views(dev):
+    """K and V living interleaved in one buffer ([T, H, slots, 2, W]) are addressed through strides."""
+    case = cases.attention_case(seq_lens=[30, 7, 70])
+    want = orc.paged_spike_attn_decode(**case)
+    d = to_dev(case, dev)
+    both = torch.stack([d["k_cache"], d["v_cache"]], dim=3).contiguous()  # [T, H, slots, 2, W]
+    d["k_cache"], d["v_cache"] = both[:, :, :, 0], both[:, :, :, 1]
+    assert not d["k_cache"].is_contiguous()
+    assert rel_err(kernels.paged_spike_attn_decode(**d).cpu(), want) < REL_TOL
+    # page-major pool with an explicit block axis: [blocks, T, H, 2, bs, W] viewed as [T, H, blocks, bs, W]
+    bs = case["block_size"]
+    nb = case["k_cache"].shape[2] // bs
+    pm = torch.empty(nb, 4, 2, 2, bs, 2, dtype=torch.int32, device=dev)
+    pm[:, :, :, 0] = to_dev(case, dev)["k_cache"].view(4, 2, nb, bs, 2).permute(2, 0, 1, 3, 4)
+    pm[:, :, :, 1] = to_dev(case, dev)["v_cache"].view(4, 2, nb, bs, 2).permute(2, 0, 1, 3, 4)
+    d["k_cache"] = pm[:, :, :, 0].permute(1, 2, 0, 3, 4)
+    d["v_cache"] = pm[:, :, :, 1].permute(1, 2, 0, 3, 4)
+    assert rel_err(kernels.paged_spike_attn_decode(**d).cpu(), want) < REL_TOL
+
+
+def test_corrupt_metadata_is_flagged_not_followed(dev):
+    """Host-side fault injection: a block id outside the pool and a bad length set status bits; the
+    kernel skips the access instead of reading out of bounds."""
+    case = cases.attention_case(seq_lens=[20, 40])
+    d = to_dev(case, dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    d["block_tables"] = d["block_tables"].clone()
+    d["block_tables"][1, 1] = 10_000
+    out = kernels.paged_spike_attn_decode(**d, status=status)
+    assert status.item() & _lib.STATUS_BAD_BLOCK
+    assert torch.isfinite(out).all()
+    ok = orc.paged_spike_attn_decode(**case)
+    assert rel_err(out[:, 0].cpu(), ok[:, 0]) < REL_TOL  # the healthy row is unaffected
+    status.zero_()
+    d = to_dev(case, dev)
+    d["seq_lens"] = torch.tensor([0, 10_000], dtype=torch.int32, device=dev)
+    out = kernels.paged_spike_attn_decode(**d, status=status)
+    assert status.item() & _lib.STATUS_BAD_SEQ_LEN
+    assert torch.isfinite(out).all() and (out[:, 0] == 0).all()
+
+
+def test_gather_kv_unpacked(dev, golden):
+    case = cases.attention_case(**cases.ATTENTION_CASES["ragged"])
+    d = to_dev(case, dev)
+    got = kernels.gather_kv_unpacked(d["k_cache"], d["block_tables"][3], 97, 64, 16, torch.float32)
+    assert torch.equal(got.cpu().to(torch.uint8), golden("attention")["gather_ragged_3"])
+    got = kernels.gather_kv_unpacked(d["v_cache"], d["block_tables"][2], 40, 64, 16, torch.bfloat16)
+    want = orc.gather_kv_unpacked(case["v_cache"], case["block_tables"][2], 40, 64, 16, torch.bfloat16)
+    assert torch.equal(got.cpu(), want)
+
+
+def config2_case(seed=2, n=64, lo=128, hi=4096):
+    g = cases.gen(seed)
+    lens = torch.randint(lo, hi + 1, (n,), generator=g).tolist()
+    return cases.attention_case(seq_lens=lens, density=0.2, seed=seed, spare_blocks=0, max_blocks=hi // 16)
+
+
+def test_config2_full_size(dev):
+    """BASELINE config 2: 64 ragged sequences in [128, 4096], 14/2 heads, D 64, T 4, Bernoulli(0.2) bits,
+    16-token pages in a shuffled pool.  fp32 vs the oracle at 1e-5; bf16 within 1e-3; scores exact on a sample;
+    and linearity in V as a size-independent property (out(V1 | V2) = out(V1) + out(V2) for disjoint V bits)."""
+    case = config2_case()
+    d = to_dev(case, dev)
+    got = kernels.paged_spike_attn_decode(**d)
+    want = orc.paged_spike_attn_decode(**case)
+    assert rel_err(got.cpu(), want) < REL_TOL
+    got16 = kernels.paged_spike_attn_decode(**d, dtype=torch.bfloat16).cpu()
+    assert rel_err(got16, want.to(torch.bfloat16)) < 2.0 ** -8 + REL_TOL_BF16
+    mask = torch.tensor([0x0F0F0F0F, 0x33333333], dtype=torch.int32, device=dev)
+    d1, d2 = dict(d), dict(d)
+    d1["v_cache"] = d["v_cache"] & mask
+    d2["v_cache"] = d["v_cache"] & ~mask
+    o1, o2 = kernels.paged_spike_attn_decode(**d1), kernels.paged_spike_attn_decode(**d2)
+    torch.testing.assert_close(o1 + o2, got, rtol=1e-5, atol=1e-6)
+    keys = ("q_packed", "k_cache", "block_tables", "seq_lens", "head_dim", "block_size", "num_q_heads", "num_kv_heads")
+    sub = {k: (case[k][:, :4] if k == "q_packed" else case[k][:4] if k in ("block_tables", "seq_lens") else case[k]) for k in keys}
+    assert torch.equal(kernels.qk_scores(**to_dev(sub, dev)).cpu(), orc.qk_scores(**sub))

@@ -1,0 +1,73 @@
+"""GPU parity: the on-device decode metadata builder against the oracle's BlockManager / prepare_decode
+(the reference's host-side allocator and runner, block_manager.py:50-77, model_runner.py:66-138)."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import torch_oracle as orc
+from spikeinfer_b200 import _lib
+from spikeinfer_b200.engine.batch_state import DecodeBatchState
+
+pytestmark = pytest.mark.gpu
+
+
+def test_trace_matches_host_allocator(dev):
+    bs, num_blocks, max_rows, max_blocks = 4, 13, 8, 8  # last block = pad
+    state = DecodeBatchState(max_rows=max_rows, max_blocks=max_blocks, num_blocks=num_blocks, block_size=bs, device=dev)
+    mgr = orc.BlockManager(num_blocks - 1, bs)
+    tables = {}
+    computed = {}
+    # admit three prefilled sequences into rows 0, 2, 5 (prompt lengths 5, 9, 2)
+    for row, plen, tok in ((0, 5, 11), (2, 9, 22), (5, 2, 33)):
+        t = []
+        assert mgr.allocate(t, 0, plen)
+        got = state.take_blocks(mgr.blocks_for(plen))
+        assert got.tolist() == t, "device free list hands out blocks in a different order"
+        state.admit(row, got, plen, tok)
+        tables[row], computed[row] = t, plen
+    assert state.free_count() == len(mgr.free_list)
+    next_tokens = torch.arange(100, 100 + max_rows, dtype=torch.int64, device=dev)
+    for step in range(7):
+        rows = sorted(tables)
+        for r in rows:  # host allocator: row order
+            assert mgr.allocate(tables[r], computed[r], 1)
+        pos, slots, bt, lens = orc.prepare_decode([tables[r] for r in rows], [computed[r] for r in rows],
+                                                  max_blocks, num_blocks - 1, bs)
+        state.next_tokens.copy_(next_tokens + step)
+        state.advance()
+        for i, r in enumerate(rows):
+            assert state.positions[r].item() == pos[i].item()
+            assert state.slot_mapping[r].item() == slots[i].item()
+            assert state.seq_lens[r].item() == lens[i].item()
+            assert state.block_tables[r].tolist() == bt[i].tolist()
+            assert state.input_ids[r].item() == 100 + r + step
+            computed[r] += 1
+        for r in range(max_rows):
+            if r not in tables:  # pad rows stay parked on the pad block, as the graph runner keeps them
+                assert state.seq_lens[r].item() == 1 and state.slot_mapping[r].item() == (num_blocks - 1) * bs
+                assert (state.block_tables[r] == num_blocks - 1).all()
+        assert state.free_count() == len(mgr.free_list)
+        assert state.free_list[: state.free_count()].tolist() == mgr.free_list
+        if step == 3:  # sequence in row 2 finishes: blocks go back in table order
+            mgr.free(tables.pop(2))
+            computed.pop(2)
+            state.release(2)
+            assert state.free_list[: state.free_count()].tolist() == mgr.free_list
+    assert state.status.item() == 0
+
+
+def test_pool_exhaustion_and_full_table_are_flagged(dev):
+    state = DecodeBatchState(max_rows=4, max_blocks=2, num_blocks=3, block_size=2, device=dev)
+    state.admit(0, state.take_blocks(1), 2, 1)  # needs a new block at the next step
+    state.admit(1, state.take_blocks(1), 2, 1)  # pool now empty
+    state.advance()
+    assert state.status.item() & _lib.STATUS_POOL_EXHAUSTED
+    assert state.seq_lens[:2].tolist() == [2, 2], "a row that got no block must not advance"
+    assert state.slot_mapping[0].item() == 2 * 2  # parked on the pad slot
+    state.status.zero_()
+    state2 = DecodeBatchState(max_rows=2, max_blocks=1, num_blocks=4, block_size=2, device=dev)
+    state2.admit(0, state2.take_blocks(1), 2, 1)
+    state2.advance()
+    assert state2.status.item() & _lib.STATUS_TABLE_FULL
+    assert state2.seq_lens[0].item() == 2

@@ -1,0 +1,253 @@
+"""GPU parity: bit packing and the LIF kernels against the CPU oracle and the golden fixtures.
+
+Everything here is bit-exact (torch.equal): packed words, spikes and the fp32 membrane.
+Mirrors tests/test_packing.py and tests/test_lif_kernel.py of the reference.
+"""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import cases
+from oracle import torch_oracle as orc
+from spikeinfer_b200 import _lib, kernels
+
+pytestmark = pytest.mark.gpu
+
+
+# ------------------------------------------------------------------ packing
+@pytest.mark.parametrize("channels", cases.PACK_CHANNELS)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.uint8])
+def test_pack_roundtrip_and_golden(channels, dtype, dev, golden):
+    x = cases.pack_case(channels)
+    words = kernels.pack_spikes(x.to(dev, dtype))
+    assert words.dtype == torch.int32 and words.shape == (3, 5, kernels.packed_width(channels))
+    assert torch.equal(words.cpu(), golden("packing")[channels]["words"])
+    back = kernels.unpack_spikes(words, channels, dtype)
+    assert back.dtype == dtype and torch.equal(back.cpu(), x.to(dtype))
+
+
+def test_pack_known_answers(dev):
+    assert kernels.pack_spikes(torch.ones(1, 32, device=dev)).item() == -1
+    assert int(kernels.pack_spikes(torch.ones(1, 33, device=dev))[0, 1]) == 1
+    graded = torch.tensor([[0.0, 0.5, 0.0, 2.0, float("nan"), -0.0]], device=dev)
+    assert kernels.pack_spikes(graded).item() == 0b011010
+    for ch in (0, 1, 31, 32, 63):
+        x = torch.zeros(1, 64, device=dev)
+        x[0, ch] = 1
+        w = kernels.pack_spikes(x)[0].cpu()
+        assert (int(w[ch // 32]) & 0xFFFFFFFF) == 1 << (ch % 32) and int(w[1 - ch // 32]) == 0
+    assert kernels.pack_spikes(torch.zeros(0, 64, device=dev)).shape == (0, 2)
+
+
+def test_pack_noncontiguous_views(dev):
+    """q/k/v reach the packer as permuted views; they are read in place."""
+    g = cases.gen(5)
+    spikes = cases.bernoulli_bits((2, 4, 8, 64), 0.5, g).to(dev)
+    view = spikes.permute(0, 2, 1, 3)
+    assert not view.is_contiguous()
+    assert torch.equal(kernels.pack_spikes(view).cpu(), orc.pack_spikes(view.cpu()))
+    sliced = spikes[:, 1:3, ::2]
+    assert torch.equal(kernels.pack_spikes(sliced).cpu(), orc.pack_spikes(sliced.cpu()))
+    transposed = spikes.transpose(-1, -2)  # channel axis not contiguous -> copied
+    assert torch.equal(kernels.pack_spikes(transposed).cpu(), orc.pack_spikes(transposed.cpu()))
+
+
+# ------------------------------------------------------------------ LIF, dense output
+def _check_lif(c, dev, out_dtype=None, reset_mode=0):
+    want_s, want_u = orc.lif_multistep(c["x"], c["beta"], c["threshold"], mem0=c["mem0"],
+                                       out_dtype=out_dtype, reset_mode=reset_mode)
+    mem0 = None if c["mem0"] is None else c["mem0"].to(dev)
+    got_s, got_u = kernels.lif_multistep(c["x"].to(dev), c["beta"].to(dev), c["threshold"].to(dev),
+                                         mem0=mem0, out_dtype=out_dtype, return_membrane=True,
+                                         reset_mode=reset_mode)
+    assert got_s.dtype == want_s.dtype and got_s.shape == want_s.shape
+    n_diff = (got_s.cpu() != want_s).sum().item()
+    assert n_diff == 0, f"{n_diff}/{want_s.numel()} spikes differ"
+    assert torch.equal(got_u.cpu(), want_u), f"membrane differs by {(got_u.cpu() - want_u).abs().max():.3e}"
+    return got_s
+
+
+@pytest.mark.parametrize("name", list(cases.LIF_CASES))
+def test_lif_cases_bit_exact(name, dev, golden):
+    c = cases.lif_case(**cases.LIF_CASES[name])
+    got = _check_lif(c, dev, out_dtype=torch.uint8)
+    assert torch.equal(kernels.pack_spikes(got).cpu(), golden("lif")[name]["packed"])
+
+
+@pytest.mark.parametrize("M", [128, 1792])
+@pytest.mark.parametrize("N", [64, 4864, 63])
+@pytest.mark.parametrize("T", [1, 2, 4, 8])
+def test_lif_sweep_bit_exact(T, N, M, dev):
+    _check_lif(cases.lif_case(T, M, N, seed=1000 * T + 10 * N + M), dev)
+
+
+def test_lif_threshold_boundary_stress(dev, golden):
+    c = cases.lif_boundary_case()
+    got = _check_lif(c, dev)
+    assert torch.equal(kernels.pack_spikes(got).cpu(), golden("lif")["boundary"]["packed"])
+
+
+def test_lif_noncontiguous_and_5d(dev):
+    g = cases.gen(7)
+    base = torch.randn(4, 64, 37, generator=g) * 2
+    c = cases.lif_case(4, 37, 64, seed=7)
+    c["x"] = base.transpose(-1, -2)  # [4, 37, 64], channel axis strided
+    _check_lif(c, dev)
+    c5 = cases.lif_case(4, 0, 64, seed=43, mid_shape=(2, 6, 5))
+    c5["x"] = c5["x"].permute(0, 1, 3, 2, 4)  # head/token axes swapped, channel axis contiguous
+    assert not c5["x"].is_contiguous()
+    _check_lif(c5, dev)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.uint8, torch.bfloat16, torch.float16, torch.float32])
+def test_lif_out_dtypes(out_dtype, dev):
+    _check_lif(cases.lif_case(4, 128, 64, seed=11), dev, out_dtype=out_dtype)
+    _check_lif(cases.lif_case(4, 64, 96, seed=12, dtype=torch.bfloat16), dev, out_dtype=out_dtype)
+    _check_lif(cases.lif_case(4, 64, 96, seed=13, dtype=torch.float16), dev, out_dtype=out_dtype)
+
+
+def test_lif_hard_zero_mode(dev):
+    # no reference counterpart ("parity unpinned"): checked against the oracle's own definition
+    _check_lif(cases.lif_case(4, 256, 200, seed=21, scale=1.0), dev, reset_mode=orc.HARD_ZERO)
+    _check_lif(cases.lif_case(8, 64, 64, seed=22, with_mem0=True), dev, reset_mode=orc.HARD_ZERO)
+
+
+def test_lif_empty_and_single(dev):
+    s = kernels.lif_multistep(torch.zeros(4, 0, 64, device=dev), torch.ones(64, device=dev), torch.ones(64, device=dev))
+    assert s.shape == (4, 0, 64)
+    _check_lif(cases.lif_case(1, 1, 1, seed=1), dev)
+
+
+# ------------------------------------------------------------------ fused LIF + pack + scatter
+def _oracle_site(x, beta, th, reset_mode=0, mem0=None):
+    """x [T, n_tok, H, N] -> dense spikes, packed words [T, n_tok, H, W], membrane [n_tok, H, N]."""
+    s, u = orc.lif_multistep(x, beta, th, mem0=mem0, out_dtype=torch.uint8, reset_mode=reset_mode)
+    return s, orc.pack_spikes(s), u
+
+
+@pytest.mark.parametrize("reset_mode", [0, 1])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_qkv_sites_match_lif_pack_index_copy(dtype, reset_mode, dev):
+    """One launch for q, k, v: q packed as [T, n, H_q, W]; k/v scattered into reference-layout pools
+    exactly as lif_multistep -> pack_spikes -> index_copy_ would (attention.py:138-139)."""
+    T, n_tok, Hq, Hkv, D, bs, n_blocks = 4, 37, 14, 2, 64, 16, 9
+    g = cases.gen(77)
+    qkv = (torch.randn(T, n_tok, (Hq + 2 * Hkv) * D, generator=g) * 1.5).to(dtype)
+    params = [(torch.rand(D, generator=g), torch.rand(D, generator=g) * 0.9 + 0.1) for _ in range(3)]
+    slots = torch.randperm(n_blocks * bs, generator=g)[:n_tok].to(torch.int64)
+    k_pool0 = torch.randint(-2**31, 2**31 - 1, (T, Hkv, n_blocks * bs, 2), generator=g, dtype=torch.int64).to(torch.int32)
+    v_pool0 = torch.randint(-2**31, 2**31 - 1, (T, Hkv, n_blocks * bs, 2), generator=g, dtype=torch.int64).to(torch.int32)
+
+    xq = qkv[..., : Hq * D].view(T, n_tok, Hq, D)
+    xk = qkv[..., Hq * D:(Hq + Hkv) * D].view(T, n_tok, Hkv, D)
+    xv = qkv[..., (Hq + Hkv) * D:].view(T, n_tok, Hkv, D)
+    want = [_oracle_site(x, b, th, reset_mode) for x, (b, th) in zip((xq, xk, xv), params)]
+    want_k = k_pool0.clone().index_copy_(2, slots, want[1][1].permute(0, 2, 1, 3).contiguous())
+    want_v = v_pool0.clone().index_copy_(2, slots, want[2][1].permute(0, 2, 1, 3).contiguous())
+
+    d = qkv.to(dev)
+    dq = d[..., : Hq * D].view(T, n_tok, Hq, D)
+    dk = d[..., Hq * D:(Hq + Hkv) * D].view(T, n_tok, Hkv, D)
+    dv = d[..., (Hq + Hkv) * D:].view(T, n_tok, Hkv, D)
+    q_packed = torch.empty(T, n_tok, Hq, 2, dtype=torch.int32, device=dev)
+    k_pool, v_pool = k_pool0.to(dev), v_pool0.to(dev)
+    q_dense = torch.empty(T, 1, Hq, n_tok, D, dtype=dtype, device=dev)  # the reference's [T,1,H,n_tok,D] layout
+    k_mem = torch.empty(n_tok, Hkv, D, dtype=torch.float32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    S = kernels.LifSiteSpec
+    kernels.lif_pack_scatter([
+        S(x=dq, beta=params[0][0].to(dev), threshold=params[0][1].to(dev), packed=q_packed,
+          packed_strides=(n_tok * Hq * 2, Hq * 2, 2), dense=q_dense,
+          dense_strides=(q_dense.stride(0), q_dense.stride(3), q_dense.stride(2))),
+        S(x=dk, beta=params[1][0].to(dev), threshold=params[1][1].to(dev), packed=k_pool,
+          packed_strides=(k_pool.stride(0), k_pool.stride(2), k_pool.stride(1)),
+          slot_mapping=slots.to(dev), num_rows=n_blocks * bs, mem_out=k_mem),
+        S(x=dv, beta=params[2][0].to(dev), threshold=params[2][1].to(dev), packed=v_pool,
+          packed_strides=(v_pool.stride(0), v_pool.stride(2), v_pool.stride(1)),
+          slot_mapping=slots.to(dev), num_rows=n_blocks * bs),
+    ], reset_mode=reset_mode, status=status)
+    assert torch.equal(q_packed.cpu(), want[0][1])
+    assert torch.equal(k_pool.cpu(), want_k), "K pool differs from lif -> pack -> index_copy_"
+    assert torch.equal(v_pool.cpu(), want_v)
+    assert torch.equal(q_dense[:, 0].permute(0, 2, 1, 3).cpu().to(torch.uint8), want[0][0])
+    assert torch.equal(k_mem.cpu(), want[1][2])
+    assert status.item() == 0
+
+
+def test_fused_gate_site_odd_width_and_mem0(dev):
+    T, n_tok, N = 4, 19, 4864 + 37  # not a multiple of 32 nor of the per-warp span
+    g = cases.gen(5)
+    x = torch.randn(T, n_tok, N, generator=g).to(torch.bfloat16)
+    beta, th = torch.rand(N, generator=g) * 2 - 0.5, torch.rand(N, generator=g) + 0.5
+    mem0 = torch.randn(n_tok, 1, N, generator=g)
+    dense_w, packed_w, mem_w = _oracle_site(x.unsqueeze(2), beta, th, mem0=mem0)
+    packed = torch.full((T, n_tok, kernels.packed_width(N)), -1, dtype=torch.int32, device=dev)
+    dense = torch.empty(T, n_tok, N, dtype=torch.bfloat16, device=dev)
+    mem = torch.empty(n_tok, 1, N, dtype=torch.float32, device=dev)
+    W = kernels.packed_width(N)
+    kernels.lif_pack_scatter([kernels.LifSiteSpec(
+        x=x.to(dev).unsqueeze(2), beta=beta.to(dev), threshold=th.to(dev), packed=packed,
+        packed_strides=(n_tok * W, W, 0), dense=dense, dense_strides=(n_tok * N, N, 0),
+        mem0=mem0.to(dev), mem_out=mem)])
+    assert torch.equal(packed.cpu(), packed_w.squeeze(2))
+    assert torch.equal(dense.cpu().to(torch.uint8), dense_w.squeeze(2))
+    assert torch.equal(mem.cpu(), mem_w)
+    p2, d2, m2 = kernels.lif_pack(x.to(dev), beta.to(dev), th.to(dev), dense_dtype=torch.uint8, return_membrane=True)
+    want_s, want_p, want_u = _oracle_site(x.unsqueeze(2), beta, th)
+    assert torch.equal(p2.cpu(), want_p.squeeze(2)) and torch.equal(d2.cpu(), want_s.squeeze(2))
+    assert torch.equal(m2.cpu(), want_u.squeeze(1))
+
+
+def test_fused_bad_slot_is_skipped_and_flagged(dev):
+    """A slot outside the pool must not be written; the status word records it (no trap)."""
+    T, n_tok, D, n_slots = 2, 4, 64, 32
+    x = torch.full((T, n_tok, 1, D), 5.0, device=dev)
+    pool = torch.zeros(T, 1, n_slots, 2, dtype=torch.int32, device=dev)
+    slots = torch.tensor([3, 32, -1, 7], dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    one = torch.ones(D, device=dev)
+    kernels.lif_pack_scatter([kernels.LifSiteSpec(
+        x=x, beta=one, threshold=one, packed=pool, packed_strides=(pool.stride(0), pool.stride(2), pool.stride(1)),
+        slot_mapping=slots, num_rows=n_slots)], status=status)
+    assert status.item() == _lib.STATUS_BAD_SLOT
+    written = (pool != 0).any(dim=-1).any(dim=0)[0].nonzero().flatten().tolist()
+    assert written == [3, 7]
+    assert (pool[:, 0, 3] == -1).all()
+
+
+def test_config3_full_size_gate_and_kv(dev):
+    """BASELINE config 3 at full size: gate [4, 8192, 4864] bf16 and k/v [4, 8192, 2x64] scattered through a
+    random slot permutation of a 16-token-page pool.  Packed bits, membrane and pool bit-exact vs the oracle."""
+    T, n_tok, N, Hkv, D, bs = 4, 8192, 4864, 2, 64, 16
+    g = cases.gen(3)
+    th = torch.rand(N, generator=g) + 0.5
+    beta = torch.full((N,), 0.9)
+    chunk = 1024  # the oracle works through the tokens in chunks to bound host memory
+    gate = torch.randn(T, n_tok, N, generator=g).to(torch.bfloat16)
+    packed, _, mem = kernels.lif_pack(gate.to(dev), beta.to(dev), th.to(dev), return_membrane=True)
+    packed, mem = packed.cpu(), mem.cpu()
+    for s in range(0, n_tok, chunk):
+        ws, wu = orc.lif_multistep(gate[:, s:s + chunk], beta, th, out_dtype=torch.uint8)
+        assert torch.equal(packed[:, s:s + chunk], orc.pack_spikes(ws))
+        assert torch.equal(mem[s:s + chunk], wu)
+    rate = orc.unpack_spikes(packed[:, :256], N).mean().item()
+    assert 0.05 < rate < 0.6
+
+    kv = torch.randn(T, n_tok, 2 * Hkv * D, generator=g).to(torch.bfloat16)
+    th_kv = torch.rand(D, generator=g) + 0.5
+    slots = torch.randperm(n_tok, generator=g).to(torch.int64)
+    k_pool = torch.zeros(T, Hkv, n_tok, 2, dtype=torch.int32, device=dev)
+    v_pool = torch.zeros_like(k_pool)
+    d = kv.to(dev)
+    S = kernels.LifSiteSpec
+    mk = lambda x, pool: S(x=x, beta=torch.full((D,), 0.9, device=dev), threshold=th_kv.to(dev), packed=pool,
+                           packed_strides=(pool.stride(0), pool.stride(2), pool.stride(1)),
+                           slot_mapping=slots.to(dev), num_rows=n_tok)
+    kernels.lif_pack_scatter([mk(d[..., : Hkv * D].view(T, n_tok, Hkv, D), k_pool),
+                              mk(d[..., Hkv * D:].view(T, n_tok, Hkv, D), v_pool)])
+    for x, pool in ((kv[..., : Hkv * D], k_pool), (kv[..., Hkv * D:], v_pool)):
+        s, _ = orc.lif_multistep(x.view(T, n_tok, Hkv, D), torch.full((D,), 0.9), th_kv, out_dtype=torch.uint8)
+        want = torch.zeros(T, Hkv, n_tok, 2, dtype=torch.int32).index_copy_(
+            2, slots, orc.pack_spikes(s).permute(0, 2, 1, 3).contiguous())
+        assert torch.equal(pool.cpu(), want)
