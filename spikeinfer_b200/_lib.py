@@ -5,12 +5,13 @@ There is no fallback: if the library is missing or a call fails, the operators r
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_uint32, c_void_p
 from pathlib import Path
 
 import torch
 
-LIB_PATH = Path(__file__).resolve().parent / "libspikeinfer_b200.so"
+LIB_PATH = Path(os.environ.get("SPIKEINFER_B200_LIB") or Path(__file__).resolve().parent / "libspikeinfer_b200.so")
 
 # element type codes (include/spikeinfer_b200.h)
 F32, BF16, F16, U8, I32 = 0, 1, 2, 3, 4

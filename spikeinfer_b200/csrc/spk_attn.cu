@@ -23,8 +23,13 @@ namespace {
 
 constexpr int kWarpsPerBlock = 4;
 constexpr int kThreads = kWarpsPerBlock * 32;
-constexpr int kStageWords = 12;  // [w0..w3][w4..w7][v0..v3]
 constexpr int kMaxSplits = 256;
+#ifndef SPK_ATTN_CHUNK_MAX
+#define SPK_ATTN_CHUNK_MAX 512
+#endif
+#ifndef SPK_ATTN_MIN_BLOCKS
+#define SPK_ATTN_MIN_BLOCKS 1
+#endif
 constexpr int kTargetWarps = 148 * 4 * 4;  // four warps per scheduler
 
 struct AttnParams {
@@ -66,7 +71,7 @@ static inline Plan make_plan(int T, int64_t n_seqs, int Hq, int Hkv, int head_di
     int64_t chunk = (max_keys + want - 1) / want;
     chunk = ((chunk + 31) / 32) * 32;
     if (chunk < 128) chunk = 128;
-    if (chunk > 512) chunk = 512;
+    if (chunk > SPK_ATTN_CHUNK_MAX) chunk = SPK_ATTN_CHUNK_MAX;
     int64_t splits = (max_keys + chunk - 1) / chunk;
     if (splits > kMaxSplits) {
         splits = kMaxSplits;
@@ -76,21 +81,51 @@ static inline Plan make_plan(int T, int64_t n_seqs, int Hq, int Hkv, int head_di
     if (splits < 1) splits = 1;
     p.splits = static_cast<int>(splits);
     p.chunk = static_cast<int>(chunk);
-    p.rec = static_cast<int64_t>(p.R) * (head_dim + 1);
+    p.rec = static_cast<int64_t>(p.R) * head_dim + 8;  // R*D sums, then R (padded to 8) weight totals
     return p;
 }
 
 template <int W>
 struct Map {
-    static constexpr int KPI = (W == 1) ? 8 : (W == 2) ? 4 : 2;  // keys per phase-B iteration
-    static constexpr int LPK = 32 / KPI;                          // lanes per key
-    static constexpr int CPL = W * KPI;                           // channels per lane
+    // Phase-B lane mapping: a key is served by LPK lanes, lane `ls` of the group owns the 8 channels
+    // of byte `ls` of the V row (word ls / 4, byte ls % 4).  KPI keys are processed per iteration.
+    static constexpr int LPK = (W == 1) ? 4 : (W == 2) ? 8 : 16;
+    static constexpr int KPI = 32 / LPK;
+    static constexpr int ITERS = 32 / KPI;
 };
+
+// Staged row of one key: the R weights (padded to a multiple of 4 words), then the V words.  The row
+// length is an odd multiple of 4 words so that both the per-key 16-byte stores of phase A and the
+// per-group 16-byte broadcast loads of phase B are free of bank conflicts.
+template <int W, int R>
+struct Row {
+    static constexpr int NQ = (R + 3) / 4;  // 16-byte loads that cover the weights
+    static constexpr int V_OFF = (R + W <= 4 * NQ) ? R : 4 * NQ;
+    static constexpr int NEED = ((V_OFF + W + 3) / 4) * 4;
+    static constexpr int WORDS = (NEED / 4) % 2 == 1 ? NEED : NEED + 4;
+};
+
+// Weights are kept multiplied by 2^kScaleLog2 so that the products below stay normal numbers.
+constexpr int kScaleLog2 = 40;
 
 __device__ __forceinline__ void store_out(void* out, int dtype, int64_t idx, float v) {
     if (dtype == SPK_F32) static_cast<float*>(out)[idx] = v;
     else if (dtype == SPK_BF16) static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
     else static_cast<__half*>(out)[idx] = __float2half_rn(v);
+}
+
+// Packed pair of fp32 values in one 64-bit register (the operand type of the f32x2 instructions).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// acc = a * b + acc on both halves (one instruction, two fp32 FMAs).
+__device__ __forceinline__ void fma2(uint64_t& acc, uint64_t a, uint64_t b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
 }
 
 // Loads the W words of one K or V row.  VEC: the row is W-word aligned and may be read with one
@@ -112,25 +147,67 @@ __device__ __forceinline__ void load_row(const uint32_t* p, bool ok, uint32_t (&
     }
 }
 
+// Phase B of one 32-key tile: every staged key is broadcast to the LPK lanes that serve it; a lane adds
+// the key's weights to the accumulators of those of its 8 channels whose V bit is set.
+//
+// The V byte a lane owns is rotated so that its 8 bits sit at bit positions 23..30 of a register;
+// masking one of those bits and reading the result as fp32 gives either 0 or the power of two
+// c_i = 2^(2^i - 127).  fma(weight, that, acc) therefore IS the bit-selected add, scaled by c_i; the
+// scale is exact (no product leaves the normal range, see kScaleLog2) and is removed once, after the
+// last key.  Two channels share one f32x2 FMA.  Measured on B200, this form beats per-bit predicated
+// adds: 47 us against 68-73 us per call at 64 sequences x [128, 4096] keys.
+template <int W, int R>
+__device__ __forceinline__ void phase_b(const uint32_t* stage, int grp, int ls, uint64_t (&acc)[R][4]) {
+    using M = Map<W>;
+    using RW = Row<W, R>;
+    const int word_off = RW::V_OFF + (ls >> 2);         // V word inside the staged row
+    const bool idle = ls >= 4 * W;                      // W == 3: lanes 12..15 own no channels
+    const int rot = (23 - 8 * (ls & 3)) & 31;           // rotate-left amount
+#pragma unroll
+    for (int it = 0; it < M::ITERS; ++it) {
+        const uint32_t* row = stage + (it * M::KPI + grp) * RW::WORDS;
+        float w[4 * RW::NQ];
+#pragma unroll
+        for (int j = 0; j < RW::NQ; ++j) {
+            const float4 t = *reinterpret_cast<const float4*>(row + 4 * j);
+            w[4 * j] = t.x; w[4 * j + 1] = t.y; w[4 * j + 2] = t.z; w[4 * j + 3] = t.w;
+        }
+        uint32_t v = idle ? 0u : row[word_off];
+        v = __funnelshift_l(v, v, rot);
+        uint64_t m[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            m[i] = pack2(__uint_as_float(v & (1u << (23 + 2 * i))), __uint_as_float(v & (1u << (24 + 2 * i))));
+#pragma unroll
+        for (int hh = 0; hh < R; ++hh) {
+            const uint64_t w2 = pack2(w[hh], w[hh]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) fma2(acc[hh][i], w2, m[i]);
+        }
+    }
+}
+
 template <int W, int R, bool VEC>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, SPK_ATTN_MIN_BLOCKS)
 attn_decode_kernel(const AttnParams p) {
     using M = Map<W>;
     constexpr int D = 32 * W;
     constexpr int LUTN = D + 1;
-    __shared__ __align__(16) uint32_t stage_all[kWarpsPerBlock][32][kStageWords];
-    __shared__ float lut_all[kWarpsPerBlock][R * LUTN];
+    using RW = Row<W, R>;
+    __shared__ __align__(16) uint32_t stage_all[kWarpsPerBlock][32 * RW::WORDS];
+    // per warp: R weight tables followed by an all-zero copy that lanes past the end of the key range read
+    __shared__ float lut_all[kWarpsPerBlock][2 * R * LUTN];
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
     if (item >= p.items) return;
 
-    // item -> (n, gp, t, c), key range fastest
+    // item -> (n, c, gp, t): timestep fastest, so the warps of a block walk the same pages
     int64_t rest = item;
-    const int c = static_cast<int>(rest % p.splits); rest /= p.splits;
     const int t = static_cast<int>(rest % p.T); rest /= p.T;
     const int gp = static_cast<int>(rest % (p.Hkv * p.passes)); rest /= (p.Hkv * p.passes);
+    const int c = static_cast<int>(rest % p.splits); rest /= p.splits;
     const int64_t n = rest;
     const int g = gp / p.passes;
     const int pass = gp - g * p.passes;
@@ -147,7 +224,7 @@ attn_decode_kernel(const AttnParams p) {
     if (begin >= len && !(len == 0 && c == 0 && p.splits == 1)) return;
     const int64_t end = min(len, begin + p.chunk_keys);
 
-    uint32_t (*stage)[kStageWords] = stage_all[warp];
+    uint32_t* stage = stage_all[warp];
     float* lut = lut_all[warp];
 
     // Query words of the heads served here, and their popcounts (the softmax bound).
@@ -163,21 +240,23 @@ attn_decode_kernel(const AttnParams p) {
             cmax[hh] += __popc(qw[hh][w]);
         }
     }
-    // Weight table: lut[hh][s] = exp((s - cmax[hh]) * scale), s <= cmax[hh].
+    // Weight table: lut[hh][s] = 2^kScaleLog2 * exp((s - cmax[hh]) * scale) for s <= cmax[hh]; the
+    // second half of the array stays zero.
+    for (int i = lane; i < R * LUTN; i += 32) lut[R * LUTN + i] = 0.0f;
 #pragma unroll
     for (int hh = 0; hh < R; ++hh) {
         for (int s = lane; s <= cmax[hh]; s += 32)
-            lut[hh * LUTN + s] = expf(static_cast<float>(s - cmax[hh]) * p.scale);
+            lut[hh * LUTN + s] = ldexpf(expf(static_cast<float>(s - cmax[hh]) * p.scale), kScaleLog2);
     }
     __syncwarp();
 
-    float acc[R][M::CPL];
+    uint64_t acc[R][4];
     float lsum[R];
 #pragma unroll
     for (int hh = 0; hh < R; ++hh) {
         lsum[hh] = 0.0f;
 #pragma unroll
-        for (int i = 0; i < M::CPL; ++i) acc[hh][i] = 0.0f;
+        for (int i = 0; i < 4; ++i) acc[hh][i] = 0ull;
     }
 
     const uint32_t* kbase = p.k + t * p.sk_t + g * p.sk_h;
@@ -185,144 +264,101 @@ attn_decode_kernel(const AttnParams p) {
     const int32_t* table = p.tables + n * p.sbt_n;
     const int bs_mask = (1 << p.bs_log2) - 1;
     const int grp = lane / M::LPK;
-    const int lsub = lane - grp * M::LPK;
+    const int ls = lane - grp * M::LPK;
 
     // Three-stage software pipeline over 32-key tiles: block-table entry of tile i+2, K/V rows of
     // tile i+1, arithmetic of tile i.
     auto table_entry = [&](int64_t key) -> int32_t {
         return key < end ? __ldg(table + (key >> p.bs_log2)) : -1;
     };
-    int32_t phys_a = table_entry(begin + lane);        // tile 0
-    int32_t phys_b = table_entry(begin + 32 + lane);   // tile 1
-    uint32_t kn[W], vn[W];
-    bool ok_n;
-    {
-        const int64_t key = begin + lane;
-        ok_n = key < end;
-        if (ok_n && (phys_a < 0 || phys_a >= p.num_blocks)) {
+    auto fetch = [&](int64_t key, int32_t phys, uint32_t (&kr)[W], uint32_t (&vr)[W]) -> bool {
+        bool ok = key < end;
+        if (ok && (phys < 0 || phys >= p.num_blocks)) {
             spk_flag(p.status, SPK_STATUS_BAD_BLOCK);
-            ok_n = false;
+            ok = false;
         }
         const int64_t slot = key & bs_mask;
-        load_row<W, VEC>(kbase + static_cast<int64_t>(phys_a) * p.sk_blk + slot * p.sk_slot, ok_n, kn);
-        load_row<W, VEC>(vbase + static_cast<int64_t>(phys_a) * p.sv_blk + slot * p.sv_slot, ok_n, vn);
-    }
+        load_row<W, VEC>(kbase + static_cast<int64_t>(phys) * p.sk_blk + slot * p.sk_slot, ok, kr);
+        load_row<W, VEC>(vbase + static_cast<int64_t>(phys) * p.sv_blk + slot * p.sv_slot, ok, vr);
+        return ok;
+    };
+    int32_t phys_b = table_entry(begin + 32 + lane);  // tile 1
+    uint32_t kn[W], vn[W];
+    bool ok_n = fetch(begin + lane, table_entry(begin + lane), kn, vn);
 
     for (int64_t tile = begin; tile < end; tile += 32) {
         uint32_t kc[W], vc[W];
 #pragma unroll
         for (int w = 0; w < W; ++w) { kc[w] = kn[w]; vc[w] = vn[w]; }
         const bool ok_c = ok_n;
-        // prefetch
         const int32_t phys_c = table_entry(tile + 64 + lane);
-        {
-            const int64_t key = tile + 32 + lane;
-            ok_n = key < end;
-            if (ok_n && (phys_b < 0 || phys_b >= p.num_blocks)) {
-                spk_flag(p.status, SPK_STATUS_BAD_BLOCK);
-                ok_n = false;
-            }
-            const int64_t slot = key & bs_mask;
-            load_row<W, VEC>(kbase + static_cast<int64_t>(phys_b) * p.sk_blk + slot * p.sk_slot, ok_n, kn);
-            load_row<W, VEC>(vbase + static_cast<int64_t>(phys_b) * p.sv_blk + slot * p.sv_slot, ok_n, vn);
-        }
+        ok_n = fetch(tile + 32 + lane, phys_b, kn, vn);
         phys_b = phys_c;
 
         // ---- phase A: lane = key ------------------------------------------------
-        float wgt[8];
+        const float* my_lut = lut + (ok_c ? 0 : R * LUTN);
+        uint32_t rowv[RW::WORDS];
 #pragma unroll
-        for (int hh = 0; hh < 8; ++hh) wgt[hh] = 0.0f;
+        for (int i = 0; i < RW::WORDS; ++i) rowv[i] = 0u;
 #pragma unroll
         for (int hh = 0; hh < R; ++hh) {
             int s = 0;
 #pragma unroll
             for (int w = 0; w < W; ++w) s += __popc(qw[hh][w] & kc[w]);
-            const float wv = ok_c ? lut[hh * LUTN + s] : 0.0f;
-            wgt[hh] = wv;
+            const float wv = my_lut[hh * LUTN + s];
+            rowv[hh] = __float_as_uint(wv);
             lsum[hh] += wv;
         }
-        uint4* row = reinterpret_cast<uint4*>(stage[lane]);
-        row[0] = make_uint4(__float_as_uint(wgt[0]), __float_as_uint(wgt[1]),
-                            __float_as_uint(wgt[2]), __float_as_uint(wgt[3]));
-        if (R > 4)
-            row[1] = make_uint4(__float_as_uint(wgt[4]), __float_as_uint(wgt[5]),
-                                __float_as_uint(wgt[6]), __float_as_uint(wgt[7]));
-        {
-            uint32_t vv[4] = {0, 0, 0, 0};
 #pragma unroll
-            for (int w = 0; w < W; ++w) vv[w] = vc[w];
-            row[2] = make_uint4(vv[0], vv[1], vv[2], vv[3]);
-        }
+        for (int w = 0; w < W; ++w) rowv[RW::V_OFF + w] = vc[w];
+        uint4* row = reinterpret_cast<uint4*>(stage + lane * RW::WORDS);
+#pragma unroll
+        for (int j = 0; j < RW::NEED / 4; ++j)
+            row[j] = make_uint4(rowv[4 * j], rowv[4 * j + 1], rowv[4 * j + 2], rowv[4 * j + 3]);
         __syncwarp();
-
-        // ---- phase B: lane = channel group, KPI keys per iteration -------------------
-        const int n_valid = (end - tile) < 32 ? static_cast<int>(end - tile) : 32;
-        const int iters = (n_valid + M::KPI - 1) / M::KPI;
-#pragma unroll 4
-        for (int it = 0; it < iters; ++it) {
-            const uint4* r = reinterpret_cast<const uint4*>(stage[it * M::KPI + grp]);
-            const uint4 a = r[0];
-            uint4 b = make_uint4(0, 0, 0, 0);
-            if (R > 4) b = r[1];
-            const uint4 vv4 = r[2];
-            const float wv[8] = {__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z),
-                                 __uint_as_float(a.w), __uint_as_float(b.x), __uint_as_float(b.y),
-                                 __uint_as_float(b.z), __uint_as_float(b.w)};
-            const uint32_t vv[4] = {vv4.x, vv4.y, vv4.z, vv4.w};
-#pragma unroll
-            for (int w = 0; w < W; ++w) {
-#pragma unroll
-                for (int i = 0; i < M::KPI; ++i) {
-                    if (vv[w] & (1u << (lsub + M::LPK * i))) {
-#pragma unroll
-                        for (int hh = 0; hh < R; ++hh) acc[hh][w * M::KPI + i] += wv[hh];
-                    }
-                }
-            }
-        }
+        // ---- phase B: lane = (key group, V byte) ---------------------------------
+        phase_b<W, R>(stage, grp, ls, acc);
         __syncwarp();
     }
 
-    // ---- reduce: weights over all lanes, accumulators over the key groups -----------
+    // ---- reduce: weights over all lanes, accumulators over the key groups; undo the scales ---
+    float out_v[R][8];
 #pragma unroll
     for (int hh = 0; hh < R; ++hh) {
 #pragma unroll
         for (int o = 16; o >= 1; o >>= 1) lsum[hh] += __shfl_xor_sync(0xffffffffu, lsum[hh], o);
 #pragma unroll
-        for (int i = 0; i < M::CPL; ++i) {
+        for (int i = 0; i < 4; ++i) unpack2(acc[hh][i], out_v[hh][2 * i], out_v[hh][2 * i + 1]);
 #pragma unroll
-            for (int o = 16; o >= M::LPK; o >>= 1)
-                acc[hh][i] += __shfl_xor_sync(0xffffffffu, acc[hh][i], o);
+        for (int i = 0; i < 8; ++i) {
+#pragma unroll
+            for (int o = 16; o >= M::LPK; o >>= 1) out_v[hh][i] += __shfl_xor_sync(0xffffffffu, out_v[hh][i], o);
+            // channel i carries the factor 2^(2^i - 127)
+            out_v[hh][i] *= __uint_as_float((254u - (1u << i)) << 23);
         }
     }
-
+    // out_v and lsum both carry the common factor 2^kScaleLog2.
+    const int d0 = (ls >> 2) * 32 + (ls & 3) * 8;
+    const bool owner = ls < 4 * W;
     if (p.splits == 1) {
 #pragma unroll
         for (int hh = 0; hh < R; ++hh) {
-            if (hh < nh && (hh % M::KPI) == grp) {
-                const int64_t o = t * p.so_t + n * p.so_n + (h0 + hh) * p.so_h;
+            if (hh < nh && owner && (hh % M::KPI) == grp) {
+                const int64_t o = t * p.so_t + n * p.so_n + (h0 + hh) * p.so_h + d0;
 #pragma unroll
-                for (int w = 0; w < W; ++w) {
-#pragma unroll
-                    for (int i = 0; i < M::KPI; ++i) {
-                        const int d = w * 32 + lsub + M::LPK * i;
-                        const float val = len > 0 ? acc[hh][w * M::KPI + i] / lsum[hh] : 0.0f;
-                        store_out(p.out, p.out_dtype, o + d, val);
-                    }
-                }
+                for (int i = 0; i < 8; ++i)
+                    store_out(p.out, p.out_dtype, o + i, len > 0 ? out_v[hh][i] / lsum[hh] : 0.0f);
             }
         }
     } else {
-        float* rec = p.ws + item * (static_cast<int64_t>(R) * (D + 1));
+        const int64_t rec_idx = ((n * (p.Hkv * p.passes) + gp) * p.T + t) * p.splits + c;
+        float* rec = p.ws + rec_idx * (static_cast<int64_t>(R) * D + 8);
 #pragma unroll
         for (int hh = 0; hh < R; ++hh) {
-            if ((hh % M::KPI) == grp) {
-#pragma unroll
-                for (int w = 0; w < W; ++w) {
-#pragma unroll
-                    for (int i = 0; i < M::KPI; ++i)
-                        rec[hh * D + w * 32 + lsub + M::LPK * i] = acc[hh][w * M::KPI + i];
-                }
+            if (owner && (hh % M::KPI) == grp) {
+                float4* o = reinterpret_cast<float4*>(rec + hh * D + d0);
+                o[0] = make_float4(out_v[hh][0], out_v[hh][1], out_v[hh][2], out_v[hh][3]);
+                o[1] = make_float4(out_v[hh][4], out_v[hh][5], out_v[hh][6], out_v[hh][7]);
             }
             if (lane == 0) rec[R * D + hh] = lsum[hh];
         }
@@ -348,7 +384,7 @@ attn_combine_kernel(const AttnParams p, int D) {
     if (len < 1) len = 0;
     if (len > max_keys) len = max_keys;
     const int n_splits = static_cast<int>((len + p.chunk_keys - 1) / p.chunk_keys);
-    const int64_t rec_floats = static_cast<int64_t>(R) * (D + 1);
+    const int64_t rec_floats = static_cast<int64_t>(R) * D + 8;
     const float* base = p.ws + grp_item * p.splits * rec_floats;
     for (int idx = threadIdx.x; idx < nh * D; idx += blockDim.x) {
         const int hh = idx / D;

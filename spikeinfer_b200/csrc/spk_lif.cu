@@ -89,8 +89,209 @@ lif_dense_kernel(const TX* __restrict__ x, int T, int64_t stride_t, SpkDims mid,
     if (mem_out != nullptr) mem_out[idx] = s.u;
 }
 
+
+constexpr int kFusedThreads = 256;
+constexpr int kStepGroup = 4;
+
 // ---------------------------------------------------------------------------
-// Fused LIF + pack + scatter.
+// Vectorised fused kernel (the fast path).
+//
+// A lane owns one segment of 8 consecutive channels of one (token, head) row and
+// reads it with a single 16-byte load per timestep (two for fp32 inputs); the
+// loads of four timesteps are in flight together.  Its 8 spike bits per timestep
+// form one byte; the four lanes of a word exchange bytes with two xor-shuffles
+// and the lane whose index matches the timestep writes the 32-bit word, so every
+// lane issues exactly one word store per group of four timesteps.  Dense spikes
+// and the membrane leave as 16/32-byte stores.  Requires N % 32 == 0 and
+// 16-byte-aligned rows; anything else takes the ballot kernel below.
+// ---------------------------------------------------------------------------
+constexpr int kSeg = 8;
+
+template <typename TX>
+struct Raw8;
+template <>
+struct Raw8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) {
+        a = __ldg(reinterpret_cast<const float4*>(p));
+        b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    }
+    __device__ __forceinline__ void clear() { a = make_float4(0, 0, 0, 0); b = a; }
+    __device__ __forceinline__ float get(int i) const {
+        switch (i) {
+            case 0: return a.x; case 1: return a.y; case 2: return a.z; case 3: return a.w;
+            case 4: return b.x; case 5: return b.y; case 6: return b.z; default: return b.w;
+        }
+    }
+};
+template <>
+struct Raw8<__nv_bfloat16> {
+    uint4 v;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = __ldg(reinterpret_cast<const uint4*>(p)); }
+    __device__ __forceinline__ void clear() { v = make_uint4(0, 0, 0, 0); }
+    __device__ __forceinline__ float get(int i) const {
+        const uint32_t w = (i >> 1) == 0 ? v.x : (i >> 1) == 1 ? v.y : (i >> 1) == 2 ? v.z : v.w;
+        // bf16 -> fp32 is exact: the 16 bits become the high half of the float
+        return __uint_as_float((i & 1) ? (w & 0xffff0000u) : (w << 16));
+    }
+};
+template <>
+struct Raw8<__half> {
+    uint4 v;
+    __device__ __forceinline__ void load(const __half* p) { v = __ldg(reinterpret_cast<const uint4*>(p)); }
+    __device__ __forceinline__ void clear() { v = make_uint4(0, 0, 0, 0); }
+    __device__ __forceinline__ float get(int i) const {
+        const uint32_t w = (i >> 1) == 0 ? v.x : (i >> 1) == 1 ? v.y : (i >> 1) == 2 ? v.z : v.w;
+        return __half2float(__ushort_as_half(static_cast<unsigned short>((i & 1) ? (w >> 16) : (w & 0xffffu))));
+    }
+};
+
+// Writes 8 spikes (bit i of `bits` = channel i of the segment) as 0/1 in the dense type.
+__device__ __forceinline__ void store_dense8(void* base, int dtype, int64_t idx, uint32_t bits) {
+    if (dtype == SPK_BF16 || dtype == SPK_F16) {
+        const uint32_t one = dtype == SPK_BF16 ? 0x3f80u : 0x3c00u;
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            w[i] = ((bits >> (2 * i)) & 1u ? one : 0u) | ((bits >> (2 * i + 1)) & 1u ? one << 16 : 0u);
+        *reinterpret_cast<uint4*>(static_cast<uint16_t*>(base) + idx) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else if (dtype == SPK_F32) {
+        float4* o = reinterpret_cast<float4*>(static_cast<float*>(base) + idx);
+        o[0] = make_float4(bits & 1u ? 1.f : 0.f, bits & 2u ? 1.f : 0.f, bits & 4u ? 1.f : 0.f, bits & 8u ? 1.f : 0.f);
+        o[1] = make_float4(bits & 16u ? 1.f : 0.f, bits & 32u ? 1.f : 0.f, bits & 64u ? 1.f : 0.f, bits & 128u ? 1.f : 0.f);
+    } else if (dtype == SPK_U8) {
+        // spread 8 bits into 8 bytes
+        const uint32_t lo = ((bits & 0xfu) * 0x00204081u) & 0x01010101u;
+        const uint32_t hi = (((bits >> 4) & 0xfu) * 0x00204081u) & 0x01010101u;
+        *reinterpret_cast<uint2*>(static_cast<uint8_t*>(base) + idx) = make_uint2(lo, hi);
+    } else {
+        int4* o = reinterpret_cast<int4*>(static_cast<int32_t*>(base) + idx);
+        o[0] = make_int4(bits & 1u, (bits >> 1) & 1u, (bits >> 2) & 1u, (bits >> 3) & 1u);
+        o[1] = make_int4((bits >> 4) & 1u, (bits >> 5) & 1u, (bits >> 6) & 1u, (bits >> 7) & 1u);
+    }
+}
+
+struct VecArgs {
+    spk_lif_site s[SPK_MAX_LIF_SITES];
+    int64_t segs[SPK_MAX_LIF_SITES];     // segments of work in each site
+    int32_t per_row[SPK_MAX_LIF_SITES];  // segments per (token, head) row
+};
+
+template <typename TX, int MODE>
+__device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, int64_t total, int per_row,
+                                               int64_t seg, int lane, int T, uint32_t* status) {
+    const bool live = seg < total;
+    const int64_t row = live ? seg / per_row : 0;
+    const int sg = live ? static_cast<int>(seg - row * per_row) : 0;
+    const int64_t tok = row / s.H;
+    const int h = static_cast<int>(row - tok * s.H);
+    const int c0 = sg * kSeg;
+
+    float b[kSeg], th[kSeg];
+    Lif st[kSeg];
+    {
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(s.beta + c0));
+        const float4 b1 = __ldg(reinterpret_cast<const float4*>(s.beta + c0) + 1);
+        const float4 t0 = __ldg(reinterpret_cast<const float4*>(s.threshold + c0));
+        const float4 t1 = __ldg(reinterpret_cast<const float4*>(s.threshold + c0) + 1);
+        const float bb[kSeg] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        const float tt[kSeg] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+        float u0[kSeg] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (live && s.mem0 != nullptr) {
+            const float4 m0 = __ldg(reinterpret_cast<const float4*>(s.mem0 + row * s.N + c0));
+            const float4 m1 = __ldg(reinterpret_cast<const float4*>(s.mem0 + row * s.N + c0) + 1);
+            u0[0] = m0.x; u0[1] = m0.y; u0[2] = m0.z; u0[3] = m0.w;
+            u0[4] = m1.x; u0[5] = m1.y; u0[6] = m1.z; u0[7] = m1.w;
+        }
+#pragma unroll
+        for (int i = 0; i < kSeg; ++i) {
+            b[i] = clamp_beta(bb[i]);
+            th[i] = tt[i];
+            st[i].init(u0[i], th[i]);
+        }
+    }
+
+    int64_t out_row = tok;
+    bool row_ok = live;
+    if (live && s.packed != nullptr && s.slot_mapping != nullptr) {
+        out_row = s.slot_mapping[tok];
+        row_ok = out_row >= 0 && out_row < s.num_rows;
+        if (!row_ok && sg == 0) spk_flag(status, SPK_STATUS_BAD_SLOT);
+    }
+    const TX* xp = static_cast<const TX*>(s.x) + tok * s.sx_tok + h * s.sx_h + c0;
+    const int sub = lane & 3;  // position of this lane's byte within its word
+
+    for (int t0 = 0; t0 < T; t0 += kStepGroup) {
+        Raw8<TX> raw[kStepGroup];
+#pragma unroll
+        for (int i = 0; i < kStepGroup; ++i) {
+            if (live && t0 + i < T) raw[i].load(xp + (t0 + i) * s.sx_t);
+            else raw[i].clear();
+        }
+        uint32_t mine = 0;
+#pragma unroll
+        for (int i = 0; i < kStepGroup; ++i) {
+            uint32_t bits = 0;
+            if (t0 + i < T) {
+#pragma unroll
+                for (int c = 0; c < kSeg; ++c)
+                    bits |= st[c].template step<MODE>(raw[i].get(c), b[c], th[c]) ? (1u << c) : 0u;
+                if (!live) bits = 0;
+                if (live && s.dense != nullptr)
+                    store_dense8(s.dense, s.dense_dtype, (t0 + i) * s.sd_t + tok * s.sd_tok + h * s.sd_h + c0, bits);
+            }
+            uint32_t word = bits << (8 * sub);
+            word |= __shfl_xor_sync(0xffffffffu, word, 1);
+            word |= __shfl_xor_sync(0xffffffffu, word, 2);
+            if (sub == i) mine = word;
+        }
+        if (s.packed != nullptr && row_ok && t0 + sub < T)
+            reinterpret_cast<uint32_t*>(s.packed)[(t0 + sub) * s.so_t + out_row * s.so_tok + h * s.so_h + (sg >> 2)] = mine;
+    }
+    if (live && s.mem_out != nullptr) {
+        float4* o = reinterpret_cast<float4*>(s.mem_out + row * s.N + c0);
+        o[0] = make_float4(st[0].u, st[1].u, st[2].u, st[3].u);
+        o[1] = make_float4(st[4].u, st[5].u, st[6].u, st[7].u);
+    }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kFusedThreads)
+lif_pack_scatter_vec_kernel(VecArgs args, int T, uint32_t* status) {
+    const int site = blockIdx.y;
+    const int lane = threadIdx.x & 31;
+    const int64_t seg = static_cast<int64_t>(blockIdx.x) * kFusedThreads + threadIdx.x;
+    if (seg - lane >= args.segs[site]) return;  // whole warp out of range
+    const spk_lif_site& s = args.s[site];
+    switch (s.x_dtype) {
+        case SPK_F32: fused_site_vec<float, MODE>(s, args.segs[site], args.per_row[site], seg, lane, T, status); break;
+        case SPK_BF16: fused_site_vec<__nv_bfloat16, MODE>(s, args.segs[site], args.per_row[site], seg, lane, T, status); break;
+        default: fused_site_vec<__half, MODE>(s, args.segs[site], args.per_row[site], seg, lane, T, status); break;
+    }
+}
+
+static inline bool is_aligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; }
+
+// Can this site take the vectorised kernel?
+static bool site_vectorisable(const spk_lif_site& s) {
+    if (s.N % 32 != 0) return false;
+    const int xs = spk_dtype_size(s.x_dtype);
+    const int64_t xq = 16 / xs;  // elements per 16 bytes
+    if (!is_aligned(s.x, 16) || s.sx_t % xq || s.sx_tok % xq || s.sx_h % xq) return false;
+    if (!is_aligned(s.beta, 16) || !is_aligned(s.threshold, 16)) return false;
+    if (s.mem0 != nullptr && !is_aligned(s.mem0, 16)) return false;
+    if (s.mem_out != nullptr && !is_aligned(s.mem_out, 16)) return false;
+    if (s.dense != nullptr) {
+        const int ds = spk_dtype_size(s.dense_dtype);
+        const int64_t bytes = ds == 1 ? 8 : 16;
+        const int64_t dq = bytes / ds;
+        if (!is_aligned(s.dense, bytes) || s.sd_t % dq || s.sd_tok % dq || s.sd_h % dq) return false;
+    }
+    return true;
+}
+
+// ---------------------------------------------------------------------------
+// Fused LIF + pack + scatter, general (ballot) form.
 //
 // A warp owns kWordsPerWarp consecutive 32-channel words of one (token, head)
 // row: lane i holds channel 32*w + i of each word, so a ballot of the spike
@@ -99,8 +300,6 @@ lif_dense_kernel(const TX* __restrict__ x, int T, int64_t stride_t, SpkDims mid,
 // word each.  K/V rows are redirected through slot_mapping on the way out.
 // ---------------------------------------------------------------------------
 constexpr int kWordsPerWarp = 2;
-constexpr int kFusedThreads = 256;
-constexpr int kStepGroup = 4;
 
 struct SiteArgs {
     spk_lif_site s[SPK_MAX_LIF_SITES];
@@ -240,6 +439,21 @@ extern "C" int spk_lif(const void* x, int x_dtype, int T, int64_t stride_t, int 
     if (x == nullptr || beta == nullptr || threshold == nullptr) return SPK_ERR_NULL_POINTER;
     if (T > 0 && spikes == nullptr) return SPK_ERR_NULL_POINTER;
     cudaStream_t s = spk_stream(stream);
+    if (n_mid <= 2 && T > 0 && (x_dtype == SPK_F32 || x_dtype == SPK_BF16 || x_dtype == SPK_F16)) {
+        // Rows addressable as (tok, h): use the vectorised kernel with a dense-only site.
+        spk_lif_site site = {};
+        site.x = x; site.x_dtype = x_dtype; site.N = N;
+        const int64_t n_tok = n_mid >= 1 ? mid.size[0] : 1;
+        site.H = static_cast<int32_t>(n_mid == 2 ? mid.size[1] : 1);
+        site.sx_t = stride_t;
+        site.sx_tok = n_mid >= 1 ? mid.stride[0] : 0;
+        site.sx_h = n_mid == 2 ? mid.stride[1] : 0;
+        site.beta = beta; site.threshold = threshold; site.mem0 = mem0; site.mem_out = mem_out;
+        site.dense = spikes; site.dense_dtype = spike_dtype;
+        site.sd_t = M * N; site.sd_tok = static_cast<int64_t>(site.H) * N; site.sd_h = N;
+        if ((n_mid < 2 || mid.size[1] <= 0x7fffffffLL) && site_vectorisable(site))
+            return spk_lif_pack_scatter(&site, 1, T, n_tok, reset_mode, nullptr, stream);
+    }
     switch (x_dtype) {
         case SPK_F32:
             return launch_dense<float>(x, T, stride_t, mid, M, N, beta, threshold, mem0, spikes,
@@ -262,6 +476,42 @@ extern "C" int spk_lif_pack_scatter(const spk_lif_site* sites, int n_sites, int 
     if (reset_mode != SPK_RESET_SUBTRACT_DELAYED && reset_mode != SPK_RESET_HARD_ZERO)
         return SPK_ERR_UNSUPPORTED;
     if (n_tok == 0) return SPK_OK;
+    bool vec = true;
+    for (int i = 0; i < n_sites; ++i) {
+        const spk_lif_site& s = sites[i];
+        if (s.x == nullptr || s.beta == nullptr || s.threshold == nullptr) return SPK_ERR_NULL_POINTER;
+        if (s.x_dtype != SPK_F32 && s.x_dtype != SPK_BF16 && s.x_dtype != SPK_F16) return SPK_ERR_BAD_DTYPE;
+        if (s.H < 1 || s.N < 1) return SPK_ERR_BAD_SHAPE;
+        if (s.dense != nullptr && spk_dtype_size(s.dense_dtype) == 0) return SPK_ERR_BAD_DTYPE;
+        if (s.packed != nullptr && s.slot_mapping != nullptr && s.num_rows < 1) return SPK_ERR_BAD_SHAPE;
+        vec = vec && site_vectorisable(s);
+    }
+    if (vec) {
+        VecArgs va;
+        int64_t max_segs = 0;
+        for (int i = 0; i < SPK_MAX_LIF_SITES; ++i) {
+            va.segs[i] = 0;
+            va.per_row[i] = 1;
+        }
+        for (int i = 0; i < n_sites; ++i) {
+            va.s[i] = sites[i];
+            const int64_t per_row = sites[i].N / kSeg;
+            if (per_row > 0x7fffffffLL) return SPK_ERR_TOO_LARGE;
+            va.per_row[i] = static_cast<int32_t>(per_row);
+            va.segs[i] = n_tok * sites[i].H * per_row;
+            if (va.segs[i] > max_segs) max_segs = va.segs[i];
+        }
+        const int64_t vblocks = (max_segs + kFusedThreads - 1) / kFusedThreads;
+        if (vblocks > 0x7fffffffLL) return SPK_ERR_TOO_LARGE;
+        dim3 vgrid(static_cast<unsigned>(vblocks), static_cast<unsigned>(n_sites));
+        cudaStream_t vst = spk_stream(stream);
+        if (reset_mode == SPK_RESET_SUBTRACT_DELAYED)
+            lif_pack_scatter_vec_kernel<SPK_RESET_SUBTRACT_DELAYED><<<vgrid, kFusedThreads, 0, vst>>>(va, T, status);
+        else
+            lif_pack_scatter_vec_kernel<SPK_RESET_HARD_ZERO><<<vgrid, kFusedThreads, 0, vst>>>(va, T, status);
+        SPK_CHECK_LAUNCH();
+        return SPK_OK;
+    }
     SiteArgs args;
     int64_t max_warps = 0;
     for (int i = 0; i < SPK_MAX_LIF_SITES; ++i) {

@@ -1,0 +1,134 @@
+"""Continuous-batching decode runner: prefill in eager mode, decode steps as one CUDA-graph replay.
+
+Plays the role of ``ModelRunner`` + ``CUDAGraphRunner`` of the reference
+(``spikeinfer/engine/model_runner.py:143-215``, ``:218-287``) for the decode path, with two
+differences: the per-step metadata is advanced on the GPU by ``DecodeBatchState.advance`` inside the
+captured graph (no host-built tensors, no buffer copies at replay), and greedy sampling (argmax) is
+captured too, so a step is a single graph launch that feeds itself.  ``step_host`` is the
+host-in-the-loop form (tokens cross PCIe both ways every step, as in the reference engine, which needs
+them for detokenisation and stop checks).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..attention import AttentionMetadata
+from ..modeling import SpikingQwenModel
+from .batch_state import DecodeBatchState
+from .spike_cache import PagedSpikeCache
+
+
+class SpikeDecodeEngine:
+    def __init__(self, model: SpikingQwenModel, num_blocks: int, block_size: int = 16, max_num_seqs: int = 64,
+                 max_model_len: int = 4096, use_graph: bool = True) -> None:
+        c = model.config
+        self.model = model
+        self.device = model.device
+        self.block_size = block_size
+        self.max_num_seqs = max_num_seqs
+        self.max_blocks = -(-max_model_len // block_size)
+        self.cache = PagedSpikeCache(c.num_hidden_layers, c.T, c.num_key_value_heads, c.head_dim, num_blocks,
+                                     block_size, device=self.device)
+        self.state = DecodeBatchState(max_num_seqs, self.max_blocks, num_blocks, block_size, device=self.device)
+        self.meta = AttentionMetadata(
+            slot_mapping=self.state.slot_mapping, block_size=block_size, num_decode_tokens=max_num_seqs,
+            block_tables=self.state.block_tables, seq_lens=self.state.seq_lens, status=self.state.status)
+        self.use_graph = use_graph
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.free_rows = list(range(max_num_seqs - 1, -1, -1))
+        self.host_in = torch.zeros(max_num_seqs, dtype=torch.int64).pin_memory()
+        self.host_out = torch.zeros(max_num_seqs, dtype=torch.int64).pin_memory()
+        self.kernel_launches_per_step = 1 + 3 * c.num_hidden_layers  # advance + (qkv site launch, attention, gate LIF)
+
+    # -- prefill ----------------------------------------------------------
+    @torch.no_grad()
+    def add_requests(self, prompts: list[list[int]]) -> list[int]:
+        """Prefill ``prompts`` in one eager batch and install them as decode rows.  Returns the rows."""
+        if len(prompts) > len(self.free_rows):
+            raise RuntimeError("no free decode row")
+        bs, dev = self.block_size, self.device
+        ids, pos, slot_parts, starts, lens, tables = [], [], [], [], [], []
+        for p in prompts:
+            n_blocks = -(-len(p) // bs)
+            table = self.state.take_blocks(n_blocks)
+            positions = torch.arange(len(p), device=dev)
+            slot_parts.append(table.to(torch.int64)[positions // bs] * bs + positions % bs)
+            starts.append(len(ids))
+            ids += p
+            pos.append(positions)
+            lens.append(len(p))
+            tables.append(table)
+        meta = AttentionMetadata(
+            slot_mapping=torch.cat(slot_parts), block_size=bs, prefill_query_starts=starts,
+            prefill_query_lens=lens, prefill_context_lens=[0] * len(lens), prefill_block_tables=tables,
+            status=self.state.status)
+        input_ids = torch.tensor(ids, dtype=torch.int64, device=dev)
+        hidden = self.model.forward_paged(input_ids, torch.cat(pos), self.cache.layers, meta)
+        last = torch.tensor([s + n - 1 for s, n in zip(starts, lens)], dtype=torch.int64, device=dev)
+        first_tokens = self.model.compute_logits(hidden, last).argmax(dim=-1)
+        rows = []
+        for i, (table, n) in enumerate(zip(tables, lens)):
+            row = self.free_rows.pop()
+            self.state.admit(row, table, n, 0)
+            rows.append(row)
+        idx = torch.tensor(rows, dtype=torch.int64, device=dev)
+        self.state.next_tokens[idx] = first_tokens
+        self.state.input_ids[idx] = first_tokens
+        return rows
+
+    def release(self, row: int) -> None:
+        self.state.release(row)
+        self.free_rows.append(row)
+
+    # -- decode -----------------------------------------------------------
+    def _body(self) -> None:
+        st = self.state
+        st.advance()
+        hidden = self.model.forward_paged(st.input_ids, st.positions, self.cache.layers, self.meta)
+        logits = self.model.compute_logits(hidden)
+        torch.argmax(logits, dim=-1, out=st.next_tokens)
+
+    @torch.no_grad()
+    def capture(self) -> None:
+        """Capture one decode step.  Warm-up runs would advance real rows, so capture happens on a
+        snapshot of the batch state and pools' pad block only: the state is saved and restored."""
+        st = self.state
+        saved = [t.clone() for t in (st.free_list, st._free_count, st.active, st.seq_lens, st.positions,
+                                     st.slot_mapping, st.block_tables, st.input_ids, st.next_tokens)]
+        active = st.active.clone()
+        st.active.zero_()  # every row is a pad row during warm-up and capture: only the pad block is written
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                self._body()
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._body()
+        for t, s in zip((st.free_list, st._free_count, st.active, st.seq_lens, st.positions, st.slot_mapping,
+                         st.block_tables, st.input_ids, st.next_tokens), saved):
+            t.copy_(s)
+        st.active.copy_(active)
+
+    @torch.no_grad()
+    def decode_step(self) -> None:
+        """One token for every active row; tokens stay on the device (``state.next_tokens``)."""
+        if self.use_graph:
+            if self.graph is None:
+                self.capture()
+            self.graph.replay()
+        else:
+            self._body()
+
+    @torch.no_grad()
+    def step_host(self, tokens_in: torch.Tensor | None = None) -> torch.Tensor:
+        """Host-in-the-loop step: ``tokens_in`` (pinned int64 ``[max_num_seqs]``, the tokens to feed) is
+        copied to the device, the step runs, and the sampled tokens are returned in pinned host memory."""
+        if tokens_in is not None:
+            self.state.next_tokens.copy_(tokens_in, non_blocking=True)
+        self.decode_step()
+        self.host_out.copy_(self.state.next_tokens, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return self.host_out

@@ -58,7 +58,7 @@ def test_host_side_argument_checks(lib):
     # split-KV plan: a short table needs no workspace, BASELINE config 2 (64 x 4096 keys) does
     assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 1) == 0
     ws = lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 256)
-    assert ws == 64 * 4 * 2 * 8 * 7 * 65 * 4
+    assert ws == 64 * 4 * 2 * 8 * (7 * 64 + 8) * 4
     assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 48, 16, 256) == 0
     # workspace required but missing -> rejected on the host, nothing launched
     big = (1, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 1, 1, _lib.F32, 0, 0, 0,
