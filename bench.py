@@ -1,0 +1,409 @@
+"""Benchmark of the spiking decode hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Headline workload ("decode_0p5b_64req"): the spiking Qwen2.5-0.5B-shape model (24 layers, hidden 896,
+14/2 heads, head_dim 64, MLP 4864, vocab 151936, tied embeddings, T=4, bf16 random-init weights,
+thresholds calibrated to ~15 % q/k/v and ~5 % gate firing), 64 concurrent requests per GPU with
+128-token random prompts, greedy decode, page size 16.  One step = one decode step of all 64 requests
+(64 tokens) as a single CUDA-graph replay: on-GPU metadata advance, 24 layers, lm_head, argmax.
+
+  value   decode tok/s with tokens looping on the device (inputs resident in HBM).
+  e2e     the same steps through ``SpikeDecodeEngine.step_host``: every step copies the input tokens
+          from pinned host memory and reads the sampled tokens back.
+  roofline  paged popcount attention kernel at the kernel-level configuration the metric names
+          (64 ragged sequences in [128, 4096], 14/2 heads, D 64, T 4, Bernoulli(0.2) bits, 16-token
+          pages, bf16 out), timed with CUDA events over 24 distinct pools back to back (430 MB of K/V,
+          larger than L2); achieved = algorithmic bytes / launch time against the measured HBM copy peak.
+  cpu_baseline  the CPU oracle port of the reference's paged model path, timed on this host's cores on
+          a bounded sample of the same workload.
+
+``--impl reference`` times that CPU port alone (the reference is pure Python/PyTorch; its CPU mode is
+what a B200-less host runs) and prints the same line with ``"impl": "reference"``.
+
+With N > 1 (launched under torchrun, one rank per GPU) every rank runs an independent replica with its
+own 64 requests and page pool (requests shard, no collective on the data path); times are the max
+over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+for _p in (str(ROOT), str(ROOT / "tests")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+METRIC = "decode_tok_per_s_0.5B_spiking_T4_64req"
+UNIT = "tok/s"
+N_REQ = 64
+PROMPT_LEN = 128
+BLOCK_SIZE = 16
+FALLBACK_HBM_GBS = 6650.0
+
+
+def hbm_peak():
+    """(GB/s, "measured" | "fallback") from MEASURED_PEAKS.json."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.samples: list[list[str]] = []
+        self.proc: subprocess.Popen | None = None
+        self.thread: threading.Thread | None = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return self
+        def pump():
+            for line in self.proc.stdout:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) == 6:
+                    self.samples.append(parts)
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()  # the exact child started above
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        mhz, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for s in self.samples:
+            try:
+                mhz.append(float(s[0]))
+                mx.append(float(s[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, s[2:]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not mhz:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(mhz), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def dist_info():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# --------------------------------------------------------------------------- workload: model + engine
+def random_weights_device(cfg, device, dtype, seed: int) -> dict:
+    """Seeded normal(0, 0.02) weights generated on the device, keyed like the reference's state_dict."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    mat = lambda *size: (torch.randn(size, generator=g, device=device, dtype=torch.float32) * 0.02).to(dtype)
+    hq, hkv, d, hid, inter = (cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.hidden_size,
+                              cfg.intermediate_size)
+    w = {"model.embed_tokens.weight": mat(cfg.vocab_size, hid), "model.norm.weight": torch.ones(hid, device=device, dtype=dtype)}
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        for name, rows in (("q", hq * d), ("k", hkv * d), ("v", hkv * d)):
+            w[p + f"self_attn.{name}_proj.weight"] = mat(rows, hid)
+            w[p + f"self_attn.{name}_proj.bias"] = torch.zeros(rows, device=device, dtype=dtype)
+            w[p + f"self_attn.lif_{name}.lif.beta"] = torch.full((d,), 0.9, device=device)
+            w[p + f"self_attn.lif_{name}.lif.threshold"] = torch.ones(d, device=device)
+        w[p + "self_attn.o_proj.weight"] = mat(hid, hq * d)
+        w[p + "mlp.gate_proj.weight"] = mat(inter, hid)
+        w[p + "mlp.up_proj.weight"] = mat(inter, hid)
+        w[p + "mlp.down_proj.weight"] = mat(hid, inter)
+        w[p + "mlp.lif_gate.lif.beta"] = torch.full((inter,), 0.9, device=device)
+        w[p + "mlp.lif_gate.lif.threshold"] = torch.ones(inter, device=device)
+        w[p + "input_layernorm.weight"] = torch.ones(hid, device=device, dtype=dtype)
+        w[p + "post_attention_layernorm.weight"] = torch.ones(hid, device=device, dtype=dtype)
+    return w
+
+
+def build_engine(device, seed: int, total_steps: int):
+    """0.5B-shape model, calibrated thresholds, 64 requests prefilled, decode graph captured."""
+    from spikeinfer_b200 import _lib
+    from spikeinfer_b200.calibrate import calibrate_thresholds
+    from spikeinfer_b200.engine.decode_engine import SpikeDecodeEngine
+    from spikeinfer_b200.modeling import SpikingQwenConfig, SpikingQwenModel
+
+    cfg = SpikingQwenConfig.qwen2_5_0p5b()
+    weights = random_weights_device(cfg, device, torch.bfloat16, seed)
+    model = SpikingQwenModel(cfg, weights, device=device)
+    del weights
+    g = torch.Generator(device="cpu").manual_seed(seed + 1)
+    prompts = torch.randint(0, cfg.vocab_size, (N_REQ, PROMPT_LEN), generator=g)
+    rates = calibrate_thresholds(model, prompts[:8].to(device))
+    model.validate_thresholds()
+    max_len = PROMPT_LEN + total_steps + 2 * BLOCK_SIZE
+    max_len = -(-max_len // 256) * 256
+    blocks_per_seq = -(-max_len // BLOCK_SIZE)
+    engine = SpikeDecodeEngine(model, num_blocks=N_REQ * blocks_per_seq + 1, block_size=BLOCK_SIZE,
+                               max_num_seqs=N_REQ, max_model_len=max_len)
+    for s in range(0, N_REQ, 16):  # prefill in groups of 16 prompts
+        engine.add_requests(prompts[s:s + 16].tolist())
+    lib = _lib.load()
+    before = lib.spk_launch_count()
+    engine.capture()
+    captured = lib.spk_launch_count() - before
+    launches_per_step = captured // 4  # three warm-up passes and the captured one
+    torch.cuda.synchronize(device)
+    engine.state.check_status()
+    return engine, rates, launches_per_step, max_len
+
+
+# --------------------------------------------------------------------------- attention roofline (kernel level)
+def attention_roofline(device, n_pools: int = 24, iters: int = 10) -> dict:
+    import cases
+    from spikeinfer_b200 import kernels
+
+    g = cases.gen(2)
+    lens = torch.randint(128, 4097, (N_REQ,), generator=g).tolist()
+    case = cases.attention_case(seq_lens=lens, density=0.2, seed=2, spare_blocks=0, max_blocks=4096 // BLOCK_SIZE)
+    d = {k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
+    pools = [(d["k_cache"].clone(), d["v_cache"].clone()) for _ in range(n_pools)]
+    out = torch.empty(4, N_REQ, 14, 64, dtype=torch.bfloat16, device=device)
+
+    def run_all():
+        for k, v in pools:
+            kernels.paged_spike_attn_decode(d["q_packed"], k, v, d["block_tables"], d["seq_lens"], 64, BLOCK_SIZE,
+                                            14, 2, out=out)
+
+    run_all()
+    torch.cuda.synchronize(device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run_all()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize(device)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize(device)
+    us = start.elapsed_time(stop) * 1e3 / (iters * n_pools)
+    sum_len = sum(lens)
+    # algorithmic bytes of one call: K+V once per KV head, q, bf16 out, block-table entries, lengths
+    alg = sum_len * 4 * 2 * 2 * 2 * 4 + 4 * N_REQ * 14 * 2 * 4 + 4 * N_REQ * 14 * 64 * 2 \
+        + sum(-(-l // BLOCK_SIZE) for l in lens) * 4 + N_REQ * 4
+    peak, which = hbm_peak()
+    achieved = alg / (us * 1e-6) / 1e9
+    return {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+            "frac": round(achieved / peak, 4), "peak_source": f"of {which}",
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this case under ncu
+            # (profiles/attn_decode_config2.md)
+            "traffic": 18.12e6,
+            "kernel": "attn_decode_kernel<W=2,R=7> (+ attn_combine_kernel)",
+            "workload": "64 seqs ragged [128,4096] (sum %d keys), 14/2 heads, D64, T4, p=0.2, page 16, bf16 out, "
+                        "%d distinct pools back to back" % (sum_len, n_pools),
+            "us_per_launch": round(us, 2), "algorithmic_bytes": alg}
+
+
+# --------------------------------------------------------------------------- CPU port of the reference path
+class CpuDecodeSample:
+    """The oracle's CPU restatement of the reference's paged model path at the 0.5B shape (fp32, as the
+    reference's pure-CPU mode), 64 requests at context 128.  The pools are filled with Bernoulli(0.15)
+    bits instead of running a CPU prefill (which alone would take minutes); every timed step is a full
+    decode step of all 64 requests: metadata build, 24 layers, lm_head, argmax."""
+
+    def __init__(self, seed: int = 0, max_len: int = 512) -> None:
+        from oracle import model_oracle as mo
+        from oracle import torch_oracle as orc
+
+        self.mo, self.orc = mo, orc
+        self.shape = mo.ModelShape(vocab_size=151936, hidden_size=896, intermediate_size=4864, num_hidden_layers=24,
+                                   num_attention_heads=14, num_key_value_heads=2, head_dim=64)
+        self.w = mo.init_weights(self.shape, seed=seed)
+        blocks_per_seq = max_len // BLOCK_SIZE
+        self.run = mo.PagedRun(self.w, self.shape, N_REQ * blocks_per_seq + 1, BLOCK_SIZE, max_len)
+        g = torch.Generator(device="cpu").manual_seed(seed + 1)
+        for _ in range(N_REQ):
+            table: list[int] = []
+            assert self.run.mgr.allocate(table, 0, PROMPT_LEN)
+            self.run.tables.append(table)
+            self.run.computed.append(PROMPT_LEN)
+            self.run.tokens.append([int(torch.randint(0, self.shape.vocab_size, (1,), generator=g))])
+        for pool in self.run.k + self.run.v:
+            bits = (torch.rand((*pool.shape[:3], 64), generator=g) < 0.15).to(torch.float32)
+            pool.copy_(orc.pack_spikes(bits))
+
+    def step(self) -> None:
+        self.run.decode()
+
+
+def time_cpu_steps(sample: CpuDecodeSample, steps: int, warmup: int) -> float:
+    for _ in range(warmup):
+        sample.step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        sample.step()
+    return (time.perf_counter() - t0) / steps
+
+
+def cpu_baseline(steps: int = 3, warmup: int = 1) -> dict:
+    sample = CpuDecodeSample()
+    sec = time_cpu_steps(sample, steps, warmup)
+    return {"value": round(N_REQ / sec, 2), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{steps} full decode steps of 64 requests at context 128 (fp32 weights, pools filled with "
+                      f"Bernoulli(0.15) bits instead of a CPU prefill), {sec:.2f} s/step after {warmup} warm-up"}
+
+
+# --------------------------------------------------------------------------- arms
+def config_dict(world: int, max_len) -> dict:
+    return {"workload": "decode_0p5b_64req: spiking Qwen2.5-0.5B shape, T=4, bf16, 64 concurrent requests per GPU, "
+                        "128-token prompts, greedy decode, page 16, CUDA-graph decode step",
+            "requests_per_gpu": N_REQ, "prompt_len": PROMPT_LEN, "block_size": BLOCK_SIZE, "max_model_len": max_len,
+            "parallelism": f"{world} independent replica(s), requests sharded, no data-path collective",
+            "l2": "inputs larger than L2: every step streams ~1 GB of weights plus the layers' pools"}
+
+
+def run_own(args) -> None:
+    import torch.distributed as dist
+
+    rank, world, local = dist_info()
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    K, W = args.steps, max(args.warmup, 3)
+    engine, rates, launches_per_step, max_len = build_engine(device, seed=1234 + rank, total_steps=2 * (K + W) + 8)
+
+    # ---- value: tokens stay on the device --------------------------------
+    for _ in range(W):
+        engine.decode_step()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local) as clocks:
+        if args.profiler_range:
+            torch.cuda.profiler.start()
+        start.record()
+        for _ in range(K):
+            engine.decode_step()
+        stop.record()
+        barrier()
+        if args.profiler_range:
+            torch.cuda.profiler.stop()
+    ms = start.elapsed_time(stop)
+    # ---- e2e: host-in-the-loop steps ---------------------------------------
+    host = engine.host_in
+    host.copy_(engine.state.next_tokens.cpu())
+    for _ in range(W):
+        host.copy_(engine.step_host(host))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        host.copy_(engine.step_host(host))
+    torch.cuda.synchronize(device)
+    e2e_s = time.perf_counter() - t0
+    engine.state.check_status()
+
+    times = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = times.tolist()
+
+    if rank == 0:
+        roof = attention_roofline(device)
+        line = {
+            "metric": METRIC, "value": round(N_REQ * K * world / (ms * 1e-3), 1), "unit": UNIT, "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": config_dict(world, max_len),
+            "e2e": {"value": round(N_REQ * K * world / (e2e_ms * 1e-3), 1), "unit": UNIT,
+                    "h2d_bytes_per_step": N_REQ * 8, "d2h_bytes_per_step": N_REQ * 8,
+                    "ms_per_step": round(e2e_ms / K, 4)},
+            "gpu_launches": launches_per_step * K,
+            "gpu_launches_per_step": launches_per_step,
+            "clocks": clocks.summary(),
+            "roofline": roof,
+            "firing_rates": {k: round(v, 3) for k, v in rates.items()},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_reference(args) -> None:
+    """The reference's CPU implementation of the path (oracle port), all host threads, rank 0 only."""
+    rank, world, _ = dist_info()
+    if rank != 0:
+        return
+    K, W = args.steps, max(args.warmup, 1)
+    sample = CpuDecodeSample(max_len=-(-(PROMPT_LEN + K + W + 16) // 256) * 256)
+    sec = time_cpu_steps(sample, K, W)
+    value = round(N_REQ / sec, 2)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": K,
+        "warmup": W, "ms_per_step": round(sec * 1e3, 2), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_dict(max(world, 1), None),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": "each step = one full decode step of 64 requests at context 128+ on the host "
+                                   "cores (fp32, pools pre-filled with Bernoulli(0.15) bits instead of a CPU prefill)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_own(args)
+
+
+if __name__ == "__main__":
+    main()

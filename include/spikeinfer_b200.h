@@ -76,6 +76,9 @@ int spk_version(void);
 int spk_last_cuda_error(void);
 /* Static description of an SPK_ERR_* code. */
 const char* spk_error_string(int code);
+/* Kernels this library has launched (or recorded into a CUDA graph being captured) in this process.
+ * No counterpart in the reference; used to report launch counts honestly. */
+int64_t spk_launch_count(void);
 
 /* ---------------------------------------------------------------------------
  * Bit packing.  Replaces pack_spikes / _pack_kernel and unpack_spikes

@@ -1,9 +1,16 @@
 // Version, error strings and per-thread launch-error bookkeeping of the C ABI.
 #include "spk_common.cuh"
 
+#include <atomic>
+
 namespace {
 thread_local int g_last_cuda_error = 0;
+std::atomic<long long> g_launches{0};
 }
+
+void spk_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+extern "C" int64_t spk_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int spk_set_cuda_error(cudaError_t err) {
     g_last_cuda_error = static_cast<int>(err);

@@ -13,10 +13,13 @@
 // Launch-error bookkeeping shared by all translation units (defined in spk_capi.cu).
 int spk_set_cuda_error(cudaError_t err);
 
+void spk_count_launch();
+
 #define SPK_CHECK_LAUNCH()                               \
     do {                                                 \
         cudaError_t e__ = cudaGetLastError();            \
         if (e__ != cudaSuccess) return spk_set_cuda_error(e__); \
+        spk_count_launch();                              \
     } while (0)
 
 static inline cudaStream_t spk_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
