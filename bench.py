@@ -232,6 +232,70 @@ def attention_roofline(device, n_pools: int = 24, iters: int = 10) -> dict:
             "us_per_launch": round(us, 2), "algorithmic_bytes": alg}
 
 
+def lif_roofline(device, n_tok: int = 8192, iters: int = 10) -> dict:
+    """Fused LIF + bit-pack (+ K/V scatter) at the kernel-level configuration: gate currents bf16
+    [T=4, n_tok, 4864] -> packed bits + fp32 membrane, and k/v currents [4, n_tok, 2x64x2] scattered through
+    a random slot permutation of a 16-token-page pool."""
+    from spikeinfer_b200 import kernels
+
+    T, N, Hkv, D = 4, 4864, 2, 64
+    g = torch.Generator(device=device).manual_seed(3)
+    gate = torch.randn((T, n_tok, N), generator=g, device=device).to(torch.bfloat16)
+    kv = torch.randn((T, n_tok, 2 * Hkv * D), generator=g, device=device).to(torch.bfloat16)
+    th = torch.rand(N, generator=g, device=device) + 0.5
+    beta = torch.full((N,), 0.9, device=device)
+    slots = torch.randperm(n_tok, generator=g, device=device)
+    k_pool = torch.zeros((T, Hkv, n_tok, 2), dtype=torch.int32, device=device)
+    v_pool = torch.zeros_like(k_pool)
+    S = kernels.LifSiteSpec
+    site = lambda x, pool: S(x=x, beta=beta[:D], threshold=th[:D], packed=pool,
+                             packed_strides=(pool.stride(0), pool.stride(2), pool.stride(1)),
+                             slot_mapping=slots, num_rows=n_tok)
+    kv_sites = [site(kv[..., : Hkv * D].unflatten(-1, (Hkv, D)), k_pool), site(kv[..., Hkv * D:].unflatten(-1, (Hkv, D)), v_pool)]
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(device)
+        start.record()
+        for _ in range(iters):
+            fn()
+        stop.record()
+        torch.cuda.synchronize(device)
+        return start.elapsed_time(stop) * 1e3 / iters
+
+    peak, which = hbm_peak()
+    out = {}
+    us = timed(lambda: kernels.lif_pack(gate, beta, th, return_membrane=True))
+    alg = gate.numel() * 2 + gate.numel() // 8 + n_tok * N * 4
+    out["gate_pack_membrane"] = {"us": round(us, 1), "algorithmic_bytes": alg, "achieved_GBs": round(alg / us / 1e3, 1),
+                                 "frac": round(alg / us / 1e3 / peak, 4)}
+    us = timed(lambda: kernels.lif_pack(gate, beta, th))
+    alg = gate.numel() * 2 + gate.numel() // 8
+    out["gate_pack"] = {"us": round(us, 1), "algorithmic_bytes": alg, "achieved_GBs": round(alg / us / 1e3, 1),
+                        "frac": round(alg / us / 1e3 / peak, 4)}
+    us = timed(lambda: kernels.lif_pack_scatter(kv_sites))
+    alg = kv.numel() * 2 + kv.numel() // 8 + n_tok * 8
+    out["kv_pack_scatter"] = {"us": round(us, 1), "algorithmic_bytes": alg, "achieved_GBs": round(alg / us / 1e3, 1),
+                              "frac": round(alg / us / 1e3 / peak, 4)}
+    out["peak"] = peak
+    out["peak_source"] = f"of {which}"
+    out["workload"] = f"T=4, {n_tok} tokens, gate 4864 channels bf16, k/v 2 heads x 64, page 16, L2 exceeded by the gate tensor"
+    return out
+
+
+def run_kernel_bench(args) -> None:
+    """Kernel-level configurations only (also the small cases the ncu captures under profiles/ run)."""
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    if args.kernel_bench == "attn":
+        res = attention_roofline(device, n_pools=args.pools, iters=args.steps)
+    else:
+        res = lif_roofline(device, n_tok=args.tokens, iters=args.steps)
+    print(json.dumps({"kernel_bench": args.kernel_bench, **res}), flush=True)
+
+
 # --------------------------------------------------------------------------- CPU port of the reference path
 class CpuDecodeSample:
     """The oracle's CPU restatement of the reference's paged model path at the 0.5B shape (fp32, as the
@@ -398,8 +462,14 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
+    ap.add_argument("--kernel-bench", choices=["attn", "lif"], default=None,
+                    help="time only the kernel-level configuration of the attention or the LIF kernel")
+    ap.add_argument("--pools", type=int, default=24, help="distinct K/V pools of --kernel-bench attn")
+    ap.add_argument("--tokens", type=int, default=8192, help="tokens of --kernel-bench lif")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.kernel_bench:
+        run_kernel_bench(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_own(args)
