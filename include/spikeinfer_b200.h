@@ -5,7 +5,8 @@
  * torch types cross this boundary.  All launches are asynchronous on the CUDA
  * stream passed as `stream` (a cudaStream_t cast to void*, NULL = legacy default
  * stream) and none of them synchronises the device, allocates device memory or
- * retains a pointer after returning, so every call may be recorded in a CUDA graph.
+ * retains a pointer after returning.  The operator entry points (spk_pack .. spk_meta_*)
+ * may therefore be recorded in a CUDA graph; spk_attn_decode_static has rules of its own.
  *
  * Return value: 0 on success, a negative SPK_ERR_* code when the arguments are
  * rejected on the host (nothing was launched), SPK_ERR_CUDA when the launch
@@ -58,6 +59,7 @@ enum {
     SPK_ERR_WORKSPACE_TOO_SMALL = -5,
     SPK_ERR_UNSUPPORTED = -6,
     SPK_ERR_TOO_LARGE = -7,
+    SPK_ERR_STATIC_SCRATCH_TOO_SMALL = -8,
     SPK_ERR_CUDA = -100
 };
 
@@ -185,6 +187,35 @@ int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int64_t sq_h,
                     int T, int64_t n_seqs, int num_q_heads, int num_kv_heads, int head_dim,
                     int block_size, int64_t max_blocks, int64_t num_blocks, float scale,
                     void* workspace, int64_t workspace_bytes, uint32_t* status, void* stream);
+
+/* spk_attn_decode for callers that cannot allocate (no counterpart in the reference).
+ *
+ * Same arguments and results as spk_attn_decode, minus the workspace: the partial sums of split
+ * rows go to a fixed SPK_ATTN_STATIC_SCRATCH_BYTES array inside the library instead.  It exists for
+ * processes that handed all free device memory to the page pool at start-up, and for hosts that
+ * drive the library through an FFI with nothing but the pointers they were given: neither can
+ * produce a workspace.  The cost is that every GPU that loads the library holds the array until
+ * the process ends.
+ *
+ *  - No cudaMalloc / cudaFree and no other allocating call is made, here or on first use.
+ *  - A problem whose spk_attn_decode_workspace_bytes() exceeds spk_attn_decode_static_capacity()
+ *    is refused with SPK_ERR_STATIC_SCRATCH_TOO_SMALL and nothing is launched (64 sequences of up
+ *    to 4096 keys at T=4, 14/2 heads, head_dim 64 need 7.5 MB and fit).
+ *  - The first call on each device looks up the array's device address (with that device current)
+ *    and remembers it; make that first call during start-up, before any stream capture begins.
+ *  - All calls on a device share the one array and it keeps whatever the last call wrote.  Nothing
+ *    in it has to start at zero (each call writes every record it later reads), but two calls
+ *    whose kernels overlap on the GPU, e.g. on different streams, race on it: serialise them. */
+#define SPK_ATTN_STATIC_SCRATCH_BYTES (8ll << 20)
+int64_t spk_attn_decode_static_capacity(void);
+int spk_attn_decode_static(const int32_t* q, int64_t sq_t, int64_t sq_n, int64_t sq_h,
+                           const int32_t* k, int64_t sk_t, int64_t sk_h, int64_t sk_blk, int64_t sk_slot,
+                           const int32_t* v, int64_t sv_t, int64_t sv_h, int64_t sv_blk, int64_t sv_slot,
+                           const int32_t* block_tables, int64_t sbt_n, const int32_t* seq_lens,
+                           void* out, int out_dtype, int64_t so_t, int64_t so_n, int64_t so_h,
+                           int T, int64_t n_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                           int block_size, int64_t max_blocks, int64_t num_blocks, float scale,
+                           uint32_t* status, void* stream);
 
 /* Exact q.k scores, for checking: scores[t, n, h, j] = popc(q[t,n,h] & k[t, h/n_rep, key j])
  * for j < seq_lens[n], -1 for seq_lens[n] <= j < max_len.  scores is contiguous int32

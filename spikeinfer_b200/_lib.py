@@ -89,6 +89,15 @@ SIGNATURES = {
         c_void_p, c_int, c_int64, c_int64, c_int64,
         c_int, c_int64, c_int, c_int, c_int, c_int, c_int64, c_int64, c_float,
         c_void_p, c_int64, c_void_p, c_void_p]),
+    "spk_attn_decode_static_capacity": (c_int64, []),
+    "spk_attn_decode_static": (c_int, [
+        c_void_p, c_int64, c_int64, c_int64,
+        c_void_p, c_int64, c_int64, c_int64, c_int64,
+        c_void_p, c_int64, c_int64, c_int64, c_int64,
+        c_void_p, c_int64, c_void_p,
+        c_void_p, c_int, c_int64, c_int64, c_int64,
+        c_int, c_int64, c_int, c_int, c_int, c_int, c_int64, c_int64, c_float,
+        c_void_p, c_void_p]),
     "spk_qk_scores": (c_int, [
         c_void_p, c_int64, c_int64, c_int64,
         c_void_p, c_int64, c_int64, c_int64, c_int64,

@@ -625,3 +625,62 @@ extern "C" int spk_gather_kv_unpacked(const int32_t* cache, int64_t s_t, int64_t
     SPK_CHECK_LAUNCH();
     return SPK_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of spk_attn_decode.
+//
+// Some callers have no way to provide the split-KV workspace: a serving process that gave every
+// remaining byte of HBM to the page pool when it started (a later cudaMalloc can fail, and it
+// synchronises the device), or a host that reaches this library through a thin FFI and only ever
+// holds the device pointers it was handed.  For them the partial sums go to a fixed array that is
+// part of the loaded module, so each GPU that loads the library carries these 8 MiB until the
+// process exits, whether or not the entry point is ever called.
+// ---------------------------------------------------------------------------
+constexpr int64_t kStaticScratchBytes = SPK_ATTN_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) float g_attn_static_scratch[kStaticScratchBytes / sizeof(float)];
+
+constexpr int kMaxDevices = 64;
+static float* g_static_scratch_ptr[kMaxDevices] = {};  // per device, filled on first use
+
+// Device address of the array on the current device.  The array's name is only a host-side handle:
+// the address a kernel can use has to be asked for, once per device, with that device current.
+static int static_scratch_for_current_device(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return spk_set_cuda_error(e);
+    if (dev < 0 || dev >= kMaxDevices) return SPK_ERR_UNSUPPORTED;
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+        if (e != cudaSuccess) return spk_set_cuda_error(e);
+        g_static_scratch_ptr[dev] = static_cast<float*>(p);
+    }
+    *out = g_static_scratch_ptr[dev];
+    return SPK_OK;
+}
+
+extern "C" int64_t spk_attn_decode_static_capacity(void) { return kStaticScratchBytes; }
+
+extern "C" int spk_attn_decode_static(const int32_t* q, int64_t sq_t, int64_t sq_n, int64_t sq_h,
+                                      const int32_t* k, int64_t sk_t, int64_t sk_h, int64_t sk_blk, int64_t sk_slot,
+                                      const int32_t* v, int64_t sv_t, int64_t sv_h, int64_t sv_blk, int64_t sv_slot,
+                                      const int32_t* block_tables, int64_t sbt_n, const int32_t* seq_lens,
+                                      void* out, int out_dtype, int64_t so_t, int64_t so_n, int64_t so_h,
+                                      int T, int64_t n_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                      int block_size, int64_t max_blocks, int64_t num_blocks, float scale,
+                                      uint32_t* status, void* stream) {
+    const int64_t need = spk_attn_decode_workspace_bytes(T, n_seqs, num_q_heads, num_kv_heads, head_dim,
+                                                         block_size, max_blocks);
+    if (need > kStaticScratchBytes) return SPK_ERR_STATIC_SCRATCH_TOO_SMALL;
+    float* scratch = nullptr;
+    if (need > 0) {
+        const int rc = static_scratch_for_current_device(&scratch);
+        if (rc != SPK_OK) return rc;
+    }
+    // Every partial record the combine pass reads is written earlier in the same call, so the
+    // array needs no clearing between calls; whatever the previous call left is never read.
+    return spk_attn_decode(q, sq_t, sq_n, sq_h, k, sk_t, sk_h, sk_blk, sk_slot, v, sv_t, sv_h, sv_blk, sv_slot,
+                           block_tables, sbt_n, seq_lens, out, out_dtype, so_t, so_n, so_h, T, n_seqs,
+                           num_q_heads, num_kv_heads, head_dim, block_size, max_blocks, num_blocks, scale,
+                           scratch, need, status, stream);
+}

@@ -31,6 +31,8 @@ extern "C" const char* spk_error_string(int code) {
         case SPK_ERR_WORKSPACE_TOO_SMALL: return "workspace missing or too small";
         case SPK_ERR_UNSUPPORTED: return "configuration not supported";
         case SPK_ERR_TOO_LARGE: return "problem exceeds a launch or capacity limit";
+        case SPK_ERR_STATIC_SCRATCH_TOO_SMALL:
+            return "problem needs more scratch than the library's built-in array holds (use spk_attn_decode with a workspace)";
         case SPK_ERR_CUDA: return "CUDA launch failed (see spk_last_cuda_error)";
         default: return "unknown error code";
     }

@@ -9,7 +9,12 @@ from .lif import (
     validate_thresholds,
 )
 from .packing import BITS_PER_WORD, pack_spikes, packed_bytes_per_token, packed_width, unpack_spikes
-from .spike_attention import gather_kv_unpacked, paged_spike_attn_decode, qk_scores
+from .spike_attention import (
+    gather_kv_unpacked,
+    paged_spike_attn_decode,
+    paged_spike_attn_decode_noalloc,
+    qk_scores,
+)
 
 __all__ = [
     "lif_multistep",
@@ -25,6 +30,7 @@ __all__ = [
     "packed_bytes_per_token",
     "BITS_PER_WORD",
     "paged_spike_attn_decode",
+    "paged_spike_attn_decode_noalloc",
     "gather_kv_unpacked",
     "qk_scores",
 ]

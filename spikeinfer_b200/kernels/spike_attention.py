@@ -140,3 +140,43 @@ def gather_kv_unpacked(cache: torch.Tensor, block_table: torch.Tensor, seq_len: 
                                         _lib.current_stream(cache.device))
     _lib.check(rc, "spk_gather_kv_unpacked")
     return out
+
+
+def paged_spike_attn_decode_noalloc(q_packed, k_cache, v_cache, block_tables, seq_lens, head_dim: int,
+                                    block_size: int, num_q_heads: int, num_kv_heads: int, out: torch.Tensor,
+                                    status: torch.Tensor | None = None) -> torch.Tensor:
+    """:func:`paged_spike_attn_decode` for callers that must not allocate.
+
+    Nothing is allocated on the way: ``out`` is required, every tensor must already be laid out as
+    the kernel wants it (no ``.contiguous()`` copies are made here), and the split-KV partial sums
+    go to the 8 MiB scratch array built into the library instead of a torch workspace.  Meant for a
+    server that gave all free device memory to the page pool at start-up, or a host that only holds
+    raw device pointers.  Problems whose partial sums do not fit raise :class:`SpkError`; calls on
+    one device share the scratch array and must not overlap on the GPU.  The first call on a device
+    resolves the array's address: make it at start-up.
+    """
+    T, n_seqs, n_heads, words = q_packed.shape
+    if words != packed_width(head_dim):
+        raise ValueError(f"q has {words} words, expected {packed_width(head_dim)}")
+    if n_heads != num_q_heads:
+        raise ValueError(f"q has {n_heads} heads, expected {num_q_heads}")
+    _lib.require_cuda(q_packed, "paged_spike_attn_decode_noalloc q_packed")
+    if q_packed.stride(3) != 1 or out.stride(3) != 1 or block_tables.stride(1) != 1 or seq_lens.stride(0) != 1:
+        raise ValueError("q_packed, out, block_tables and seq_lens must have a contiguous last axis")
+    if block_tables.dtype != torch.int32 or seq_lens.dtype != torch.int32:
+        raise TypeError("block_tables and seq_lens must be int32")
+    sk = _pool_strides(k_cache, block_size)
+    sv = _pool_strides(v_cache, block_size)
+    dev = q_packed.device
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        rc = lib.spk_attn_decode_static(
+            q_packed.data_ptr(), q_packed.stride(0), q_packed.stride(1), q_packed.stride(2),
+            k_cache.data_ptr(), sk[0], sk[1], sk[2], sk[3],
+            v_cache.data_ptr(), sv[0], sv[1], sv[2], sv[3],
+            block_tables.data_ptr(), block_tables.stride(0), seq_lens.data_ptr(),
+            out.data_ptr(), _lib.dtype_code(out.dtype), out.stride(0), out.stride(1), out.stride(2),
+            T, n_seqs, num_q_heads, num_kv_heads, head_dim, block_size, block_tables.shape[1], min(sk[4], sv[4]),
+            1.0 / math.sqrt(head_dim), _lib.ptr(status), _lib.current_stream(dev))
+    _lib.check(rc, "spk_attn_decode_static")
+    return out
