@@ -151,7 +151,7 @@ def random_weights_device(cfg, device, dtype, seed: int) -> dict:
     return w
 
 
-def build_engine(device, seed: int, total_steps: int):
+def build_engine(device, seed: int, total_steps: int, rank: int = 0, world: int = 1):
     """0.5B-shape model, calibrated thresholds, 64 requests prefilled, decode graph captured."""
     from spikeinfer_b200 import _lib
     from spikeinfer_b200.calibrate import calibrate_thresholds
@@ -162,8 +162,12 @@ def build_engine(device, seed: int, total_steps: int):
     weights = random_weights_device(cfg, device, torch.bfloat16, seed)
     model = SpikingQwenModel(cfg, weights, device=device)
     del weights
+    from spikeinfer_b200.engine.replicas import shard_requests
+
     g = torch.Generator(device="cpu").manual_seed(seed + 1)
-    prompts = torch.randint(0, cfg.vocab_size, (N_REQ, PROMPT_LEN), generator=g)
+    all_prompts = torch.randint(0, cfg.vocab_size, (N_REQ * world, PROMPT_LEN), generator=g)
+    mine = shard_requests(N_REQ * world, world, rank)  # this replica's share of the job's requests
+    prompts = all_prompts[mine.start:mine.stop]
     rates = calibrate_thresholds(model, prompts[:8].to(device))
     model.validate_thresholds()
     max_len = PROMPT_LEN + total_steps + 2 * BLOCK_SIZE
@@ -371,7 +375,8 @@ def run_own(args) -> None:
         torch.cuda.synchronize(device)
 
     K, W = args.steps, max(args.warmup, 3)
-    engine, rates, launches_per_step, max_len = build_engine(device, seed=1234 + rank, total_steps=2 * (K + W) + 8)
+    engine, rates, launches_per_step, max_len = build_engine(device, seed=1234, total_steps=2 * (K + W) + 8,
+                                                             rank=rank, world=world)
 
     # ---- value: tokens stay on the device --------------------------------
     for _ in range(W):
@@ -402,10 +407,9 @@ def run_own(args) -> None:
     e2e_s = time.perf_counter() - t0
     engine.state.check_status()
 
-    times = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = times.tolist()
+    from spikeinfer_b200.engine.replicas import max_over_ranks
+
+    ms, e2e_ms = max_over_ranks([ms, e2e_s * 1e3], device)
 
     if rank == 0:
         roof = attention_roofline(device)

@@ -128,7 +128,8 @@ int spk_lif(const void* x, int x_dtype, int T, int64_t stride_t, int n_mid,
  * row = slot_mapping[tok] when slot_mapping != NULL (rows outside [0, num_rows)
  * are skipped and flagged), else row = tok.  dense (optional) receives the 0/1
  * spikes at dense + t*sd_t + tok*sd_tok + h*sd_h + c in dense_dtype.  mem0 /
- * mem_out (optional) are contiguous fp32 [n_tok, H, N].
+ * mem_out (optional) are contiguous fp32 [n_tok, H, N].  The rope_* and mul/gated fields need
+ * N % 32 == 0 and 16-byte-aligned rows (SPK_ERR_UNSUPPORTED otherwise).
  * ------------------------------------------------------------------------- */
 #define SPK_MAX_LIF_SITES 4
 
@@ -150,10 +151,33 @@ typedef struct spk_lif_site {
     int32_t dense_dtype;
     int32_t _pad;
     int64_t sd_t, sd_tok, sd_h;
+    /* Optional rotary embedding applied to the currents before the neuron (q and k sites):
+     * cos/sin [n_tok, N] in the dtype of x, row stride s_rope_tok.  Arithmetic is
+     * (x * cos) + (rotate_half(x) * sin) with every operation rounded to that dtype, as
+     * _apply_rope_t does (spikeinfer/modeling_fast.py:89-99).  NULL = none. */
+    const void* rope_cos;
+    const void* rope_sin;
+    int64_t s_rope_tok;
+    /* Optional gated product (the MLP's gate_spk * up_proj(x), modeling_fast.py:190):
+     * gated[t, tok, h, c] = spike ? mul[t, tok, h, c] : 0, both in the dtype of x.  NULL = none. */
+    const void* mul;
+    int64_t sm_t, sm_tok, sm_h;
+    void* gated;
+    int64_t sg_t, sg_tok, sg_h;
 } spk_lif_site;
 
 int spk_lif_pack_scatter(const spk_lif_site* sites, int n_sites, int T, int64_t n_tok,
                          int reset_mode, uint32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Residual add + RMSNorm.  Replaces `h = h + delta` and the Qwen2RMSNorm call of a decoder layer
+ * (spikeinfer/modeling_fast.py:206-211, :319).  h [rows, hidden] (contiguous, updated in place when
+ * delta != NULL: h <- round(h + delta)), out [rows, hidden] = weight * (h * rsqrt(mean(h^2) + eps))
+ * with the variance in fp32 and the normalised value rounded to the dtype before the weight, as
+ * Qwen2RMSNorm does.  out may not alias h.
+ * ------------------------------------------------------------------------- */
+int spk_add_rmsnorm(void* h, const void* delta, const void* weight, float eps, void* out, int64_t rows,
+                    int64_t hidden, int dtype, void* stream);
 
 /* ---------------------------------------------------------------------------
  * Paged popcount decode attention.  Replaces paged_spike_attn_decode /

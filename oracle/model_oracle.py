@@ -126,6 +126,7 @@ def forward_paged(w: dict, shape: ModelShape, input_ids, positions, k_caches, v_
         q = q.view(T, n_tok, hq, d).permute(0, 2, 1, 3)
         k = k.view(T, n_tok, hkv, d).permute(0, 2, 1, 3)
         v = v.view(T, n_tok, hkv, d).permute(0, 2, 1, 3)
+        q_pre, k_pre = q, k
         q = (q * cos_b) + (rotate_half(q) * sin_b)
         k = (k * cos_b) + (rotate_half(k) * sin_b)
         spikes = {}
@@ -134,7 +135,8 @@ def forward_paged(w: dict, shape: ModelShape, input_ids, positions, k_caches, v_
                                      w[p + f"self_attn.lif_{name}.lif.threshold"])
             spikes[name] = s
         if capture is not None:
-            capture[i] = dict(q_cur=q, k_cur=k, v_cur=v, **{f"{n}_spk": s for n, s in spikes.items()})
+            capture[i] = dict(q_cur=q, k_cur=k, v_cur=v, q_pre=q_pre, k_pre=k_pre, cos=cos, sin=sin,
+                              **{f"{n}_spk": s for n, s in spikes.items()})
         ctx = paged_attention(spikes["q"], spikes["k"], spikes["v"], k_caches[i], v_caches[i], meta, hq, hkv, d)
         h = h + F.linear(ctx, w[p + "self_attn.o_proj.weight"])
         x = rms_norm(h, w[p + "post_attention_layernorm.weight"], shape.rms_norm_eps)

@@ -65,6 +65,17 @@ class LifSite(Structure):
         ("sd_t", c_int64),
         ("sd_tok", c_int64),
         ("sd_h", c_int64),
+        ("rope_cos", c_void_p),
+        ("rope_sin", c_void_p),
+        ("s_rope_tok", c_int64),
+        ("mul", c_void_p),
+        ("sm_t", c_int64),
+        ("sm_tok", c_int64),
+        ("sm_h", c_int64),
+        ("gated", c_void_p),
+        ("sg_t", c_int64),
+        ("sg_tok", c_int64),
+        ("sg_h", c_int64),
     ]
 
 
@@ -80,6 +91,7 @@ SIGNATURES = {
     "spk_lif": (c_int, [c_void_p, c_int, c_int, c_int64, c_int, I64P, I64P, c_int64, c_void_p,
                         c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]),
     "spk_lif_pack_scatter": (c_int, [POINTER(LifSite), c_int, c_int, c_int64, c_int, c_void_p, c_void_p]),
+    "spk_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "spk_attn_decode_workspace_bytes": (c_int64, [c_int, c_int64, c_int, c_int, c_int, c_int, c_int64]),
     "spk_attn_decode": (c_int, [
         c_void_p, c_int64, c_int64, c_int64,

@@ -105,13 +105,16 @@ def paged_attention(q_spk, k_spk, v_spk, k_cache, v_cache, meta: AttentionMetada
 
 
 def fused_qkv_attention(qkv: torch.Tensor, lif_q, lif_k, lif_v, k_cache, v_cache, meta: AttentionMetadata,
-                        num_q_heads: int, num_kv_heads: int, head_dim: int, reset_mode: int = 0) -> torch.Tensor:
-    """Attention from the (RoPE-rotated) projection outputs ``qkv [T, n_tok, (H_q + 2 H_kv) * head_dim]``.
+                        num_q_heads: int, num_kv_heads: int, head_dim: int, reset_mode: int = 0,
+                        rope: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
+    """Attention from the projection outputs ``qkv [T, n_tok, (H_q + 2 H_kv) * head_dim]``.
 
     One launch runs the LIF recurrence of the q, k and v sites, packs the spikes and scatters K/V
     straight into the pools through ``meta.slot_mapping``; the decode rows then go to the popcount
     kernel.  Dense q spikes are produced only when the batch holds prefill chunks.  ``lif_*`` are
-    ``(beta, threshold)`` pairs.  Returns ``[T, n_tok, H_q * head_dim]`` in ``qkv.dtype``.
+    ``(beta, threshold)`` pairs.  ``rope = (cos, sin)``, each ``[n_tok, head_dim]`` in ``qkv.dtype``, applies the
+    rotary embedding to the q and k currents inside the same launch; without it ``qkv`` must already be
+    rotated.  Returns ``[T, n_tok, H_q * head_dim]`` in ``qkv.dtype``.
     """
     T, n_tok, _ = qkv.shape
     dtype, device = qkv.dtype, qkv.device
@@ -126,11 +129,12 @@ def fused_qkv_attention(qkv: torch.Tensor, lif_q, lif_k, lif_v, k_cache, v_cache
         q_dense = torch.empty((T, hq, n_tok, d), dtype=dtype, device=device)
     kc, vc = _flat_pool(k_cache), _flat_pool(v_cache)
     num_slots = kc.shape[2]
+    cos, sin = rope if rope is not None else (None, None)
     lif_pack_scatter([
-        LifSiteSpec(x=xq, beta=lif_q[0], threshold=lif_q[1], packed=q_packed,
+        LifSiteSpec(x=xq, beta=lif_q[0], threshold=lif_q[1], packed=q_packed, rope_cos=cos, rope_sin=sin,
                     packed_strides=(n_tok * hq * W, hq * W, W), dense=q_dense,
                     dense_strides=None if q_dense is None else (q_dense.stride(0), q_dense.stride(2), q_dense.stride(1))),
-        LifSiteSpec(x=xk, beta=lif_k[0], threshold=lif_k[1], packed=kc,
+        LifSiteSpec(x=xk, beta=lif_k[0], threshold=lif_k[1], packed=kc, rope_cos=cos, rope_sin=sin,
                     packed_strides=(kc.stride(0), kc.stride(2), kc.stride(1)),
                     slot_mapping=meta.slot_mapping, num_rows=num_slots),
         LifSiteSpec(x=xv, beta=lif_v[0], threshold=lif_v[1], packed=vc,

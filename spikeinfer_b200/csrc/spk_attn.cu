@@ -108,6 +108,13 @@ struct Row {
 // Weights are kept multiplied by 2^kScaleLog2 so that the products below stay normal numbers.
 constexpr int kScaleLog2 = 40;
 
+// Keys per range of a row of `len` keys cut into at most `splits` ranges of whole tiles.
+__device__ __forceinline__ int64_t row_range_keys(int64_t len, int splits) {
+    const int64_t tiles = (len + 31) >> 5;
+    const int64_t n = tiles < splits ? (tiles > 0 ? tiles : 1) : splits;
+    return ((tiles + n - 1) / n) << 5;
+}
+
 __device__ __forceinline__ void store_out(void* out, int dtype, int64_t idx, float v) {
     if (dtype == SPK_F32) static_cast<float*>(out)[idx] = v;
     else if (dtype == SPK_BF16) static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
@@ -220,9 +227,12 @@ attn_decode_kernel(const AttnParams p) {
         if (lane == 0 && c == 0) spk_flag(p.status, SPK_STATUS_BAD_SEQ_LEN);
         len = len < 1 ? 0 : max_keys;
     }
-    const int64_t begin = static_cast<int64_t>(c) * p.chunk_keys;
+    // A row is cut into up to `splits` equal key ranges of whole 32-key tiles, whatever its length:
+    // short rows are spread over several warps too (short critical path when the GPU is underfilled).
+    const int64_t range = row_range_keys(len, p.splits);
+    const int64_t begin = static_cast<int64_t>(c) * range;
     if (begin >= len && !(len == 0 && c == 0 && p.splits == 1)) return;
-    const int64_t end = min(len, begin + p.chunk_keys);
+    const int64_t end = min(len, begin + range);
 
     uint32_t* stage = stage_all[warp];
     float* lut = lut_all[warp];
@@ -240,16 +250,6 @@ attn_decode_kernel(const AttnParams p) {
             cmax[hh] += __popc(qw[hh][w]);
         }
     }
-    // Weight table: lut[hh][s] = 2^kScaleLog2 * exp((s - cmax[hh]) * scale) for s <= cmax[hh]; the
-    // second half of the array stays zero.
-    for (int i = lane; i < R * LUTN; i += 32) lut[R * LUTN + i] = 0.0f;
-#pragma unroll
-    for (int hh = 0; hh < R; ++hh) {
-        for (int s = lane; s <= cmax[hh]; s += 32)
-            lut[hh * LUTN + s] = ldexpf(expf(static_cast<float>(s - cmax[hh]) * p.scale), kScaleLog2);
-    }
-    __syncwarp();
-
     uint64_t acc[R][4];
     float lsum[R];
 #pragma unroll
@@ -285,6 +285,18 @@ attn_decode_kernel(const AttnParams p) {
     int32_t phys_b = table_entry(begin + 32 + lane);  // tile 1
     uint32_t kn[W], vn[W];
     bool ok_n = fetch(begin + lane, table_entry(begin + lane), kn, vn);
+
+    // (built after the first loads were issued, so their latency overlaps the exponentials)
+    // Weight table: lut[hh][s] = 2^kScaleLog2 * exp((s - cmax[hh]) * scale) for s <= cmax[hh]; the
+    // second half of the array stays zero.
+    for (int i = lane; i < R * LUTN; i += 32) lut[R * LUTN + i] = 0.0f;
+#pragma unroll
+    for (int hh = 0; hh < R; ++hh) {
+        for (int s = lane; s <= cmax[hh]; s += 32)
+            lut[hh * LUTN + s] = ldexpf(expf(static_cast<float>(s - cmax[hh]) * p.scale), kScaleLog2);
+    }
+    __syncwarp();
+
 
     for (int64_t tile = begin; tile < end; tile += 32) {
         uint32_t kc[W], vc[W];
@@ -383,7 +395,8 @@ attn_combine_kernel(const AttnParams p, int D) {
     const int64_t max_keys = p.max_blocks << p.bs_log2;
     if (len < 1) len = 0;
     if (len > max_keys) len = max_keys;
-    const int n_splits = static_cast<int>((len + p.chunk_keys - 1) / p.chunk_keys);
+    const int64_t range = row_range_keys(len, p.splits);
+    const int n_splits = static_cast<int>((len + range - 1) / range);
     const int64_t rec_floats = static_cast<int64_t>(R) * D + 8;
     const float* base = p.ws + grp_item * p.splits * rec_floats;
     for (int idx = threadIdx.x; idx < nh * D; idx += blockDim.x) {

@@ -146,6 +146,42 @@ struct Raw8<__half> {
     }
 };
 
+
+// Rounds an fp32 value to the element type TX and back (what a torch elementwise op in that dtype does).
+template <typename TX>
+__device__ __forceinline__ float round_to(float v);
+template <>
+__device__ __forceinline__ float round_to<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float round_to<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+template <>
+__device__ __forceinline__ float round_to<__half>(float v) { return __half2float(__float2half_rn(v)); }
+
+// Packs 8 fp32 values (already representable in TX) into the 16/32 bytes of a dense TX row segment.
+template <typename TX>
+__device__ __forceinline__ void store8(TX* p, const float (&v)[8]);
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float (&v)[8]) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = (__float_as_uint(v[2 * i]) >> 16) | (__float_as_uint(v[2 * i + 1]) & 0xffff0000u);
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <>
+__device__ __forceinline__ void store8<__half>(__half* p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        w[i] = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(v[2 * i]))) |
+               (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(v[2 * i + 1]))) << 16);
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // Writes 8 spikes (bit i of `bits` = channel i of the segment) as 0/1 in the dense type.
 __device__ __forceinline__ void store_dense8(void* base, int dtype, int64_t idx, uint32_t bits) {
     if (dtype == SPK_BF16 || dtype == SPK_F16) {
@@ -173,22 +209,26 @@ __device__ __forceinline__ void store_dense8(void* base, int dtype, int64_t idx,
 
 struct VecArgs {
     spk_lif_site s[SPK_MAX_LIF_SITES];
-    int64_t segs[SPK_MAX_LIF_SITES];     // segments of work in each site
-    int32_t per_row[SPK_MAX_LIF_SITES];  // segments per (token, head) row
+    uint32_t units[SPK_MAX_LIF_SITES];    // lanes of work in each site = token groups * per_tok
+    uint32_t per_tok[SPK_MAX_LIF_SITES];  // segments per token = H * per_row
+    uint32_t per_row[SPK_MAX_LIF_SITES];  // segments per (token, head) row = N / 8
+    int32_t toks;                          // consecutive tokens a lane walks (amortises the parameter loads)
 };
 
-template <typename TX, int MODE>
-__device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, int64_t total, int per_row,
-                                               int64_t seg, int lane, int T, uint32_t* status) {
-    const bool live = seg < total;
-    const int64_t row = live ? seg / per_row : 0;
-    const int sg = live ? static_cast<int>(seg - row * per_row) : 0;
-    const int64_t tok = row / s.H;
-    const int h = static_cast<int>(row - tok * s.H);
-    const int c0 = sg * kSeg;
+template <typename TX, int MODE, bool ROPE>
+__device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t units, uint32_t per_tok,
+                                               uint32_t per_row, int toks, uint32_t unit, int lane, int T,
+                                               int64_t n_tok, uint32_t* status) {
+    // 32-bit index arithmetic only: one lane = (token group, head, 8-channel segment)
+    const bool in_range = unit < units;
+    const uint32_t u_ = in_range ? unit : 0u;
+    const uint32_t grp = u_ / per_tok;
+    const uint32_t idx = u_ - grp * per_tok;
+    const uint32_t h = s.H == 1 ? 0u : idx / per_row;
+    const uint32_t sg = idx - h * per_row;
+    const int c0 = static_cast<int>(sg) * kSeg;
 
     float b[kSeg], th[kSeg];
-    Lif st[kSeg];
     {
         const float4 b0 = __ldg(reinterpret_cast<const float4*>(s.beta + c0));
         const float4 b1 = __ldg(reinterpret_cast<const float4*>(s.beta + c0) + 1);
@@ -196,77 +236,140 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, int64_t to
         const float4 t1 = __ldg(reinterpret_cast<const float4*>(s.threshold + c0) + 1);
         const float bb[kSeg] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
         const float tt[kSeg] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
-        float u0[kSeg] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (live && s.mem0 != nullptr) {
-            const float4 m0 = __ldg(reinterpret_cast<const float4*>(s.mem0 + row * s.N + c0));
-            const float4 m1 = __ldg(reinterpret_cast<const float4*>(s.mem0 + row * s.N + c0) + 1);
-            u0[0] = m0.x; u0[1] = m0.y; u0[2] = m0.z; u0[3] = m0.w;
-            u0[4] = m1.x; u0[5] = m1.y; u0[6] = m1.z; u0[7] = m1.w;
-        }
 #pragma unroll
         for (int i = 0; i < kSeg; ++i) {
             b[i] = clamp_beta(bb[i]);
             th[i] = tt[i];
-            st[i].init(u0[i], th[i]);
         }
     }
-
-    int64_t out_row = tok;
-    bool row_ok = live;
-    if (live && s.packed != nullptr && s.slot_mapping != nullptr) {
-        out_row = s.slot_mapping[tok];
-        row_ok = out_row >= 0 && out_row < s.num_rows;
-        if (!row_ok && sg == 0) spk_flag(status, SPK_STATUS_BAD_SLOT);
-    }
-    const TX* xp = static_cast<const TX*>(s.x) + tok * s.sx_tok + h * s.sx_h + c0;
     const int sub = lane & 3;  // position of this lane's byte within its word
+    // rotary embedding: channel c pairs with c + N/2 (first half, negated partner) or c - N/2 (second half)
+    const bool rope = ROPE && s.rope_cos != nullptr;
+    const bool first_half = 2 * sg < per_row;
+    const int64_t partner_off = first_half ? s.N / 2 : -(s.N / 2);
+    const float partner_sign = first_half ? -1.0f : 1.0f;
 
-    for (int t0 = 0; t0 < T; t0 += kStepGroup) {
-        Raw8<TX> raw[kStepGroup];
-#pragma unroll
-        for (int i = 0; i < kStepGroup; ++i) {
-            if (live && t0 + i < T) raw[i].load(xp + (t0 + i) * s.sx_t);
-            else raw[i].clear();
-        }
-        uint32_t mine = 0;
-#pragma unroll
-        for (int i = 0; i < kStepGroup; ++i) {
-            uint32_t bits = 0;
-            if (t0 + i < T) {
-#pragma unroll
-                for (int c = 0; c < kSeg; ++c)
-                    bits |= st[c].template step<MODE>(raw[i].get(c), b[c], th[c]) ? (1u << c) : 0u;
-                if (!live) bits = 0;
-                if (live && s.dense != nullptr)
-                    store_dense8(s.dense, s.dense_dtype, (t0 + i) * s.sd_t + tok * s.sd_tok + h * s.sd_h + c0, bits);
+    for (int j = 0; j < toks; ++j) {
+        const int64_t tok = static_cast<int64_t>(grp) * toks + j;
+        const bool live = in_range && tok < n_tok;
+        const int64_t row = tok * s.H + h;
+        Lif st[kSeg];
+        {
+            float u0[kSeg] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (live && s.mem0 != nullptr) {
+                const float4 m0 = __ldg(reinterpret_cast<const float4*>(s.mem0 + row * s.N + c0));
+                const float4 m1 = __ldg(reinterpret_cast<const float4*>(s.mem0 + row * s.N + c0) + 1);
+                u0[0] = m0.x; u0[1] = m0.y; u0[2] = m0.z; u0[3] = m0.w;
+                u0[4] = m1.x; u0[5] = m1.y; u0[6] = m1.z; u0[7] = m1.w;
             }
-            uint32_t word = bits << (8 * sub);
-            word |= __shfl_xor_sync(0xffffffffu, word, 1);
-            word |= __shfl_xor_sync(0xffffffffu, word, 2);
-            if (sub == i) mine = word;
+#pragma unroll
+            for (int i = 0; i < kSeg; ++i) st[i].init(u0[i], th[i]);
         }
-        if (s.packed != nullptr && row_ok && t0 + sub < T)
-            reinterpret_cast<uint32_t*>(s.packed)[(t0 + sub) * s.so_t + out_row * s.so_tok + h * s.so_h + (sg >> 2)] = mine;
-    }
-    if (live && s.mem_out != nullptr) {
-        float4* o = reinterpret_cast<float4*>(s.mem_out + row * s.N + c0);
-        o[0] = make_float4(st[0].u, st[1].u, st[2].u, st[3].u);
-        o[1] = make_float4(st[4].u, st[5].u, st[6].u, st[7].u);
+        int64_t out_row = tok;
+        bool row_ok = live;
+        if (live && s.packed != nullptr && s.slot_mapping != nullptr) {
+            out_row = s.slot_mapping[tok];
+            row_ok = out_row >= 0 && out_row < s.num_rows;
+            if (!row_ok && sg == 0) spk_flag(status, SPK_STATUS_BAD_SLOT);
+        }
+        const TX* xp = static_cast<const TX*>(s.x) + tok * s.sx_tok + static_cast<int64_t>(h) * s.sx_h + c0;
+        float rc[kSeg], rs[kSeg];
+        if (rope) {
+            Raw8<TX> cr, sr;
+            if (live) {
+                cr.load(static_cast<const TX*>(s.rope_cos) + tok * s.s_rope_tok + c0);
+                sr.load(static_cast<const TX*>(s.rope_sin) + tok * s.s_rope_tok + c0);
+            } else {
+                cr.clear();
+                sr.clear();
+            }
+#pragma unroll
+            for (int c = 0; c < kSeg; ++c) { rc[c] = cr.get(c); rs[c] = sr.get(c); }
+        }
+
+        for (int t0 = 0; t0 < T; t0 += kStepGroup) {
+            Raw8<TX> raw[kStepGroup], partner[kStepGroup], mulv[kStepGroup];
+            const bool gated = live && s.gated != nullptr;
+#pragma unroll
+            for (int i = 0; i < kStepGroup; ++i) {
+                if (live && t0 + i < T) raw[i].load(xp + (t0 + i) * s.sx_t);
+                else raw[i].clear();
+                if (gated && t0 + i < T)
+                    mulv[i].load(static_cast<const TX*>(s.mul) + (t0 + i) * s.sm_t + tok * s.sm_tok +
+                                 static_cast<int64_t>(h) * s.sm_h + c0);
+                else mulv[i].clear();
+                if (rope) {
+                    if (live && t0 + i < T) partner[i].load(xp + (t0 + i) * s.sx_t + partner_off);
+                    else partner[i].clear();
+                }
+            }
+            uint32_t mine = 0;
+#pragma unroll
+            for (int i = 0; i < kStepGroup; ++i) {
+                uint32_t bits = 0;
+                if (t0 + i < T) {
+#pragma unroll
+                    for (int c = 0; c < kSeg; ++c) {
+                        float cur = raw[i].get(c);
+                        if (rope) {
+                            // (x * cos) + (rotate_half(x) * sin), every operation rounded to the model dtype
+                            const float a = round_to<TX>(__fmul_rn(cur, rc[c]));
+                            const float r = round_to<TX>(__fmul_rn(partner_sign * partner[i].get(c), rs[c]));
+                            cur = round_to<TX>(__fadd_rn(a, r));
+                        }
+                        bits |= st[c].template step<MODE>(cur, b[c], th[c]) ? (1u << c) : 0u;
+                    }
+                    if (!live) bits = 0;
+                    if (gated) {
+                        // gated[t, tok, h, c] = spike ? mul[t, tok, h, c] : 0   (the spike * up product)
+                        float g[kSeg];
+#pragma unroll
+                        for (int c = 0; c < kSeg; ++c) g[c] = (bits >> c) & 1u ? mulv[i].get(c) : 0.0f;
+                        store8<TX>(static_cast<TX*>(s.gated) + (t0 + i) * s.sg_t + tok * s.sg_tok +
+                                   static_cast<int64_t>(h) * s.sg_h + c0, g);
+                    }
+                    if (live && s.dense != nullptr)
+                        store_dense8(s.dense, s.dense_dtype,
+                                     (t0 + i) * s.sd_t + tok * s.sd_tok + static_cast<int64_t>(h) * s.sd_h + c0, bits);
+                }
+                uint32_t word = bits << (8 * sub);
+                word |= __shfl_xor_sync(0xffffffffu, word, 1);
+                word |= __shfl_xor_sync(0xffffffffu, word, 2);
+                if (sub == i) mine = word;
+            }
+            if (s.packed != nullptr && row_ok && t0 + sub < T)
+                reinterpret_cast<uint32_t*>(s.packed)[(t0 + sub) * s.so_t + out_row * s.so_tok +
+                                                      static_cast<int64_t>(h) * s.so_h + (sg >> 2)] = mine;
+        }
+        if (live && s.mem_out != nullptr) {
+            float4* o = reinterpret_cast<float4*>(s.mem_out + row * s.N + c0);
+            o[0] = make_float4(st[0].u, st[1].u, st[2].u, st[3].u);
+            o[1] = make_float4(st[4].u, st[5].u, st[6].u, st[7].u);
+        }
     }
 }
 
-template <int MODE>
+template <int MODE, bool ROPE>
 __global__ void __launch_bounds__(kFusedThreads)
-lif_pack_scatter_vec_kernel(VecArgs args, int T, uint32_t* status) {
+lif_pack_scatter_vec_kernel(VecArgs args, int T, int64_t n_tok, uint32_t* status) {
     const int site = blockIdx.y;
     const int lane = threadIdx.x & 31;
-    const int64_t seg = static_cast<int64_t>(blockIdx.x) * kFusedThreads + threadIdx.x;
-    if (seg - lane >= args.segs[site]) return;  // whole warp out of range
+    const uint32_t unit = blockIdx.x * kFusedThreads + threadIdx.x;
+    if (unit - lane >= args.units[site]) return;  // whole warp out of range
     const spk_lif_site& s = args.s[site];
     switch (s.x_dtype) {
-        case SPK_F32: fused_site_vec<float, MODE>(s, args.segs[site], args.per_row[site], seg, lane, T, status); break;
-        case SPK_BF16: fused_site_vec<__nv_bfloat16, MODE>(s, args.segs[site], args.per_row[site], seg, lane, T, status); break;
-        default: fused_site_vec<__half, MODE>(s, args.segs[site], args.per_row[site], seg, lane, T, status); break;
+        case SPK_F32:
+            fused_site_vec<float, MODE, ROPE>(s, args.units[site], args.per_tok[site], args.per_row[site], args.toks,
+                                        unit, lane, T, n_tok, status);
+            break;
+        case SPK_BF16:
+            fused_site_vec<__nv_bfloat16, MODE, ROPE>(s, args.units[site], args.per_tok[site], args.per_row[site],
+                                                args.toks, unit, lane, T, n_tok, status);
+            break;
+        default:
+            fused_site_vec<__half, MODE, ROPE>(s, args.units[site], args.per_tok[site], args.per_row[site], args.toks,
+                                         unit, lane, T, n_tok, status);
+            break;
     }
 }
 
@@ -281,6 +384,14 @@ static bool site_vectorisable(const spk_lif_site& s) {
     if (!is_aligned(s.beta, 16) || !is_aligned(s.threshold, 16)) return false;
     if (s.mem0 != nullptr && !is_aligned(s.mem0, 16)) return false;
     if (s.mem_out != nullptr && !is_aligned(s.mem_out, 16)) return false;
+    if (s.rope_cos != nullptr) {
+        if (s.rope_sin == nullptr || !is_aligned(s.rope_cos, 16) || !is_aligned(s.rope_sin, 16) || s.s_rope_tok % xq)
+            return false;
+    }
+    if (s.gated != nullptr) {
+        if (s.mul == nullptr || !is_aligned(s.mul, 16) || !is_aligned(s.gated, 16)) return false;
+        if (s.sm_t % xq || s.sm_tok % xq || s.sm_h % xq || s.sg_t % xq || s.sg_tok % xq || s.sg_h % xq) return false;
+    }
     if (s.dense != nullptr) {
         const int ds = spk_dtype_size(s.dense_dtype);
         const int64_t bytes = ds == 1 ? 8 : 16;
@@ -488,29 +599,53 @@ extern "C" int spk_lif_pack_scatter(const spk_lif_site* sites, int n_sites, int 
     }
     if (vec) {
         VecArgs va;
-        int64_t max_segs = 0;
+        // tokens per lane: 4 once that still leaves every SM a few thousand lanes, else 2 or 1
+        int64_t widest = 0;
+        for (int i = 0; i < n_sites; ++i) widest = widest > sites[i].H * (sites[i].N / kSeg) ? widest : sites[i].H * (sites[i].N / kSeg);
+        int toks = 4;
+        while (toks > 1 && (n_tok / toks) * widest < 148LL * 2048) toks >>= 1;
+        va.toks = toks;
+        const int64_t groups = (n_tok + toks - 1) / toks;
+        int64_t max_units = 0;
         for (int i = 0; i < SPK_MAX_LIF_SITES; ++i) {
-            va.segs[i] = 0;
+            va.units[i] = 0;
+            va.per_tok[i] = 1;
             va.per_row[i] = 1;
         }
+        bool fits = true;
         for (int i = 0; i < n_sites; ++i) {
             va.s[i] = sites[i];
             const int64_t per_row = sites[i].N / kSeg;
-            if (per_row > 0x7fffffffLL) return SPK_ERR_TOO_LARGE;
-            va.per_row[i] = static_cast<int32_t>(per_row);
-            va.segs[i] = n_tok * sites[i].H * per_row;
-            if (va.segs[i] > max_segs) max_segs = va.segs[i];
+            const int64_t per_tok = per_row * sites[i].H;
+            const int64_t units = groups * per_tok;
+            if (units >= 0x7fffffffLL) fits = false;
+            va.per_row[i] = static_cast<uint32_t>(per_row);
+            va.per_tok[i] = static_cast<uint32_t>(per_tok);
+            va.units[i] = static_cast<uint32_t>(units);
+            if (units > max_units) max_units = units;
         }
-        const int64_t vblocks = (max_segs + kFusedThreads - 1) / kFusedThreads;
-        if (vblocks > 0x7fffffffLL) return SPK_ERR_TOO_LARGE;
-        dim3 vgrid(static_cast<unsigned>(vblocks), static_cast<unsigned>(n_sites));
-        cudaStream_t vst = spk_stream(stream);
-        if (reset_mode == SPK_RESET_SUBTRACT_DELAYED)
-            lif_pack_scatter_vec_kernel<SPK_RESET_SUBTRACT_DELAYED><<<vgrid, kFusedThreads, 0, vst>>>(va, T, status);
-        else
-            lif_pack_scatter_vec_kernel<SPK_RESET_HARD_ZERO><<<vgrid, kFusedThreads, 0, vst>>>(va, T, status);
-        SPK_CHECK_LAUNCH();
-        return SPK_OK;
+        if (fits) {
+            const int64_t vblocks = (max_units + kFusedThreads - 1) / kFusedThreads;
+            dim3 vgrid(static_cast<unsigned>(vblocks), static_cast<unsigned>(n_sites));
+            cudaStream_t vst = spk_stream(stream);
+            bool any_rope = false;
+            for (int i = 0; i < n_sites; ++i) any_rope = any_rope || sites[i].rope_cos != nullptr;
+            const bool sub = reset_mode == SPK_RESET_SUBTRACT_DELAYED;
+            if (sub && any_rope)
+                lif_pack_scatter_vec_kernel<SPK_RESET_SUBTRACT_DELAYED, true><<<vgrid, kFusedThreads, 0, vst>>>(va, T, n_tok, status);
+            else if (sub)
+                lif_pack_scatter_vec_kernel<SPK_RESET_SUBTRACT_DELAYED, false><<<vgrid, kFusedThreads, 0, vst>>>(va, T, n_tok, status);
+            else if (any_rope)
+                lif_pack_scatter_vec_kernel<SPK_RESET_HARD_ZERO, true><<<vgrid, kFusedThreads, 0, vst>>>(va, T, n_tok, status);
+            else
+                lif_pack_scatter_vec_kernel<SPK_RESET_HARD_ZERO, false><<<vgrid, kFusedThreads, 0, vst>>>(va, T, n_tok, status);
+            SPK_CHECK_LAUNCH();
+            return SPK_OK;
+        }
+    }
+    for (int i = 0; i < n_sites; ++i) {
+        // the rotary and gated-product fusions exist only in the vectorised kernel
+        if (sites[i].rope_cos != nullptr || sites[i].gated != nullptr) return SPK_ERR_UNSUPPORTED;
     }
     SiteArgs args;
     int64_t max_warps = 0;

@@ -38,7 +38,6 @@ class SpikeDecodeEngine:
         self.free_rows = list(range(max_num_seqs - 1, -1, -1))
         self.host_in = torch.zeros(max_num_seqs, dtype=torch.int64).pin_memory()
         self.host_out = torch.zeros(max_num_seqs, dtype=torch.int64).pin_memory()
-        self.kernel_launches_per_step = 1 + 3 * c.num_hidden_layers  # advance + (qkv site launch, attention, gate LIF)
 
     # -- prefill ----------------------------------------------------------
     @torch.no_grad()

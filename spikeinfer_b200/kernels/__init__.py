@@ -3,11 +3,13 @@ from .lif import (
     HARD_ZERO,
     SUBTRACT_DELAYED,
     LifSiteSpec,
+    lif_gate_mul,
     lif_multistep,
     lif_pack,
     lif_pack_scatter,
     validate_thresholds,
 )
+from .norm import add_rms_norm
 from .packing import BITS_PER_WORD, pack_spikes, packed_bytes_per_token, packed_width, unpack_spikes
 from .spike_attention import (
     gather_kv_unpacked,
@@ -21,6 +23,8 @@ __all__ = [
     "validate_thresholds",
     "lif_pack_scatter",
     "lif_pack",
+    "lif_gate_mul",
+    "add_rms_norm",
     "LifSiteSpec",
     "SUBTRACT_DELAYED",
     "HARD_ZERO",

@@ -113,6 +113,13 @@ class LifSiteSpec:
     dense_strides: tuple[int, int, int] | None = None
     mem0: torch.Tensor | None = None
     mem_out: torch.Tensor | None = None
+    rope_cos: torch.Tensor | None = None
+    """Optional ``[n_tok, N]`` cos / sin (dtype of ``x``): rotary embedding applied to the currents first."""
+    rope_sin: torch.Tensor | None = None
+    mul: torch.Tensor | None = None
+    """Optional ``[T, n_tok, H, N]`` (dtype of ``x``, any strides with a contiguous channel axis)."""
+    gated: torch.Tensor | None = None
+    """Output of the gated product ``spike ? mul : 0``, same shape and dtype as ``mul``."""
 
 
 def lif_pack_scatter(sites: list[LifSiteSpec], reset_mode: int = SUBTRACT_DELAYED,
@@ -162,6 +169,20 @@ def lif_pack_scatter(sites: list[LifSiteSpec], reset_mode: int = SUBTRACT_DELAYE
             e.dense = s.dense.data_ptr()
             e.dense_dtype = _lib.dtype_code(s.dense.dtype)
             e.sd_t, e.sd_tok, e.sd_h = s.dense_strides
+        if s.rope_cos is not None:
+            cos, sin = s.rope_cos, s.rope_sin
+            if cos.dtype != x.dtype or sin.dtype != x.dtype or cos.shape != (n_tok, N) or sin.shape != (n_tok, N):
+                raise ValueError(f"site {i}: rope cos/sin must be [n_tok, N] in the dtype of x")
+            if cos.stride(1) != 1 or sin.stride(1) != 1 or cos.stride(0) != sin.stride(0):
+                raise ValueError(f"site {i}: rope cos/sin must share a row stride and have contiguous rows")
+            e.rope_cos, e.rope_sin, e.s_rope_tok = cos.data_ptr(), sin.data_ptr(), cos.stride(0)
+        if s.gated is not None:
+            for name, t in (("mul", s.mul), ("gated", s.gated)):
+                if t is None or t.dtype != x.dtype or t.shape != x.shape or t.stride(3) != 1:
+                    raise ValueError(f"site {i}: {name} must match x in shape and dtype with a contiguous channel axis")
+            e.mul, e.gated = s.mul.data_ptr(), s.gated.data_ptr()
+            e.sm_t, e.sm_tok, e.sm_h = s.mul.stride(0), s.mul.stride(1), s.mul.stride(2)
+            e.sg_t, e.sg_tok, e.sg_h = s.gated.stride(0), s.gated.stride(1), s.gated.stride(2)
     if n_tok == 0 or T == 0:
         return
     lib = _lib.load()
@@ -187,3 +208,14 @@ def lif_pack(x: torch.Tensor, beta: torch.Tensor, threshold: torch.Tensor, *, de
     )
     lif_pack_scatter([site], reset_mode=reset_mode)
     return packed, dense, mem
+
+
+def lif_gate_mul(gate: torch.Tensor, up: torch.Tensor, beta: torch.Tensor, threshold: torch.Tensor,
+                 reset_mode: int = SUBTRACT_DELAYED) -> torch.Tensor:
+    """``lif_multistep(gate) * up`` in one launch: ``[T, n_tok, N]`` currents and multiplicand (strided views of
+    one GEMM output are fine) -> contiguous ``[T, n_tok, N]`` product; the dense spikes are never written."""
+    T, n_tok, N = gate.shape
+    out = torch.empty((T, n_tok, N), dtype=gate.dtype, device=gate.device)
+    lif_pack_scatter([LifSiteSpec(x=gate.unsqueeze(2), beta=beta, threshold=threshold, mul=up.unsqueeze(2),
+                                  gated=out.unsqueeze(2))], reset_mode=reset_mode)
+    return out

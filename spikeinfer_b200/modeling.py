@@ -10,10 +10,13 @@ the hot-path call sites replaced:
   (:func:`spikeinfer_b200.attention.fused_qkv_attention`) instead of three ``lif_multistep``, three
   ``pack_spikes`` and two ``index_copy_`` (``modeling_fast.py:132-134``, ``attention.py:138-148``);
 * decode rows attend through the popcount kernel;
-* the gate LIF and the ``gate_spk * up_proj(x)`` product (``modeling_fast.py:186-190``) use the fused
-  LIF kernel's dense output.
+* RoPE (``modeling_fast.py:89-99``) is applied to the q and k currents inside that launch, with every
+  operation rounded to the model dtype as the eager expression does;
+* the gate LIF and the ``gate_spk * up_proj(x)`` product (``modeling_fast.py:186-190``) are one launch
+  that never writes the dense gate spikes;
+* each residual add + RMSNorm pair is one launch.
 
-Dense GEMMs, RMSNorm and RoPE stay PyTorch (cuBLAS and elementwise kernels).  Weights are a
+Dense GEMMs stay PyTorch (cuBLAS), as do the embedding lookup, the final mean over T and argmax.  Weights are a
 ``dict[str, Tensor]`` keyed exactly like the reference's ``state_dict``.
 """
 from __future__ import annotations
@@ -25,7 +28,7 @@ import torch.nn.functional as F
 
 from . import _lib
 from .attention import AttentionMetadata, fused_qkv_attention
-from .kernels import lif_multistep
+from .kernels import add_rms_norm, lif_gate_mul
 
 
 @dataclass
@@ -124,24 +127,20 @@ class SpikingQwenModel:
         hq, hkv, d = c.num_attention_heads, c.num_key_value_heads, c.head_dim
         n_tok = input_ids.shape[0]
         embeds = F.embedding(input_ids, self.embed)
-        cos, sin = self.rope(positions)
-        cos, sin = cos[None, :, None, :], sin[None, :, None, :]  # over [T, n_tok, H, D]
+        rope = self.rope(positions)  # (cos, sin), each [n_tok, D]
         h = embeds.unsqueeze(0).expand(T, n_tok, -1).contiguous()
-        n_rot = hq + hkv
+        delta = None
         for i, L in enumerate(self.layers):
-            x = rms_norm(h, L["ln1"], c.rms_norm_eps)
+            x = add_rms_norm(h, delta, L["ln1"], c.rms_norm_eps)  # h <- h + delta, x = norm(h)
             qkv = F.linear(x, L["w_qkv"], L["b_qkv"])  # [T, n_tok, (hq + 2 hkv) d]
-            qk = qkv[..., : n_rot * d].unflatten(-1, (n_rot, d))
-            qkv[..., : n_rot * d] = ((qk * cos) + (rotate_half(qk) * sin)).flatten(-2)
             ctx = fused_qkv_attention(qkv, L["lif_q"], L["lif_k"], L["lif_v"], kv_caches[i][0], kv_caches[i][1],
-                                      meta, hq, hkv, d)
-            h = h + F.linear(ctx, L["w_o"])
-            x = rms_norm(h, L["ln2"], c.rms_norm_eps)
+                                      meta, hq, hkv, d, rope=rope)
+            delta = F.linear(ctx, L["w_o"])
+            x = add_rms_norm(h, delta, L["ln2"], c.rms_norm_eps)
             gu = F.linear(x, L["w_gate_up"])  # [T, n_tok, 2 * inter]
-            gate, up = gu[..., : c.intermediate_size], gu[..., c.intermediate_size:]
-            gate_spk = lif_multistep(gate, L["lif_gate"][0], L["lif_gate"][1])
-            h = h + F.linear(gate_spk * up, L["w_down"])
-        return rms_norm(h, self.norm, c.rms_norm_eps).mean(dim=0)
+            act = lif_gate_mul(gu[..., : c.intermediate_size], gu[..., c.intermediate_size:], *L["lif_gate"])
+            delta = F.linear(act, L["w_down"])
+        return add_rms_norm(h, delta, self.norm, c.rms_norm_eps).mean(dim=0)
 
     @torch.no_grad()
     def compute_logits(self, hidden: torch.Tensor, indices: torch.Tensor | None = None) -> torch.Tensor:

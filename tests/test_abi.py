@@ -37,7 +37,7 @@ def test_version_and_error_strings(lib):
 
 def test_site_struct_layout():
     # 3 pointers/ints block + strides: must match `spk_lif_site` (all members 8-byte aligned)
-    assert ctypes.sizeof(_lib.LifSite) == 8 + 4 + 4 + 8 + 24 + 32 + 8 + 24 + 8 + 8 + 8 + 4 + 4 + 24
+    assert ctypes.sizeof(_lib.LifSite) == 8 + 4 + 4 + 8 + 24 + 32 + 8 + 24 + 8 + 8 + 8 + 4 + 4 + 24 + 24 + 32 + 32
 
 
 def test_host_side_argument_checks(lib):

@@ -67,6 +67,13 @@ def test_per_layer_operators_bit_exact_on_oracle_tensors(variant, dev, golden):
             kc, vc = k_before[i].to(dev), v_before[i].to(dev)
             ctx = fused_qkv_attention(qkv.to(dev), *lif, kc, vc, meta, hq, hkv, d)
             assert torch.equal(kc.cpu(), run.k[i]), f"{step} layer {i}: K pool differs"
+            # same launch with the rotary embedding fused: un-rotated currents in, identical pools out
+            pre = torch.cat([c[n].permute(0, 2, 1, 3).reshape(T, n_tok, -1) for n in ("q_pre", "k_pre", "v_cur")], dim=-1)
+            kc3, vc3 = k_before[i].to(dev), v_before[i].to(dev)
+            ctx3 = fused_qkv_attention(pre.to(dev), *lif, kc3, vc3, meta, hq, hkv, d,
+                                       rope=(c["cos"].to(dev), c["sin"].to(dev)))
+            assert torch.equal(kc3, kc) and torch.equal(vc3, vc), f"{step} layer {i}: fused RoPE changed the pools"
+            assert torch.equal(ctx3, ctx)
             assert torch.equal(vc.cpu(), run.v[i]), f"{step} layer {i}: V pool differs"
             err = (ctx.cpu() - c["ctx"]).abs().max() / c["ctx"].abs().max().clamp(min=1e-6)
             assert err < 1e-5, f"{step} layer {i}: context rel err {err:.2e}"
@@ -79,6 +86,9 @@ def test_per_layer_operators_bit_exact_on_oracle_tensors(variant, dev, golden):
             pg = f"model.layers.{i}.mlp.lif_gate.lif."
             gate = kernels.lif_multistep(c["gate_cur"].to(dev), w[pg + "beta"].to(dev), w[pg + "threshold"].to(dev))
             assert torch.equal(gate.cpu(), c["gate_spk"]), f"{step} layer {i}: gate spikes differ"
+            up = torch.randn(c["gate_cur"].shape, generator=cases.gen(i))
+            prod = kernels.lif_gate_mul(c["gate_cur"].to(dev), up.to(dev), w[pg + "beta"].to(dev), w[pg + "threshold"].to(dev))
+            assert torch.equal(prod.cpu(), c["gate_spk"] * up + 0.0), f"{step} layer {i}: gated product differs"
 
 
 @pytest.mark.parametrize("use_graph", [False, True])

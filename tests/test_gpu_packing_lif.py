@@ -251,3 +251,59 @@ def test_config3_full_size_gate_and_kv(dev):
         want = torch.zeros(T, Hkv, n_tok, 2, dtype=torch.int32).index_copy_(
             2, slots, orc.pack_spikes(s).permute(0, 2, 1, 3).contiguous())
         assert torch.equal(pool.cpu(), want)
+
+
+# ------------------------------------------------------------------ fused RoPE, gated product, add + RMSNorm
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_fused_rope_is_bit_exact_with_the_eager_expression(dtype, dev):
+    """(x * cos) + (rotate_half(x) * sin), every op rounded to the model dtype (modeling_fast.py:89-99), then LIF."""
+    T, n_tok, H, D = 4, 29, 3, 64
+    g = cases.gen(91)
+    x = (torch.randn(T, n_tok, H, D, generator=g) * 1.5).to(dtype)
+    pos = torch.randint(0, 4000, (n_tok,), generator=g)
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.cat([pos.float()[:, None] * inv[None, :]] * 2, dim=-1)
+    cos, sin = ang.cos().to(dtype), ang.sin().to(dtype)
+    rot = torch.cat((-x[..., D // 2:], x[..., : D // 2]), dim=-1)
+    want_cur = (x * cos[None, :, None, :]) + (rot * sin[None, :, None, :])
+    beta, th = torch.rand(D, generator=g), torch.rand(D, generator=g) * 0.9 + 0.1
+    want_s, want_u = orc.lif_multistep(want_cur, beta, th, out_dtype=torch.uint8)
+    packed = torch.empty(T, n_tok, H, 2, dtype=torch.int32, device=dev)
+    mem = torch.empty(n_tok, H, D, device=dev)
+    kernels.lif_pack_scatter([kernels.LifSiteSpec(
+        x=x.to(dev), beta=beta.to(dev), threshold=th.to(dev), packed=packed, packed_strides=(n_tok * H * 2, H * 2, 2),
+        mem_out=mem, rope_cos=cos.to(dev), rope_sin=sin.to(dev))])
+    assert torch.equal(packed.cpu(), orc.pack_spikes(want_s))
+    assert torch.equal(mem.cpu(), want_u)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gated_product_on_strided_gemm_output(dtype, dev):
+    T, n_tok, N = 4, 21, 4864
+    g = cases.gen(17)
+    gu = torch.randn(T, n_tok, 2 * N, generator=g).to(dtype)  # [gate | up] as one GEMM writes them
+    beta, th = torch.full((N,), 0.9), torch.rand(N, generator=g) + 0.3
+    s, _ = orc.lif_multistep(gu[..., :N], beta, th)
+    want = s * gu[..., N:]
+    d = gu.to(dev)
+    got = kernels.lif_gate_mul(d[..., :N], d[..., N:], beta.to(dev), th.to(dev))
+    assert got.is_contiguous() and torch.equal(got.cpu(), want + 0.0)  # + 0.0: -0 and +0 compare equal anyway
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 2.0 ** -6)])  # bf16: two roundings -> 2 steps
+def test_add_rms_norm(dtype, tol, dev):
+    from oracle import model_oracle as mo
+
+    g = cases.gen(23)
+    h = torch.randn(4, 37, 896, generator=g).to(dtype)
+    delta = (torch.randn(4, 37, 896, generator=g) * 0.3).to(dtype)
+    w = (torch.rand(896, generator=g) + 0.5).to(dtype)
+    want_h = h + delta
+    want = mo.rms_norm(want_h, w, 1e-6)
+    dh = h.to(dev)
+    got = kernels.add_rms_norm(dh, delta.to(dev), w.to(dev), 1e-6)
+    assert torch.equal(dh.cpu(), want_h), "the residual must be updated in place, rounded as the eager add"
+    err = ((got.cpu().float() - want.float()).abs() / want.float().abs().clamp(min=1e-3)).max().item()
+    assert err <= tol, f"rel err {err:.2e}"
+    got2 = kernels.add_rms_norm(dh, None, w.to(dev), 1e-6)
+    assert torch.equal(got2, got) and torch.equal(dh.cpu(), want_h)
