@@ -162,9 +162,13 @@ __device__ __forceinline__ void load_row(const uint32_t* p, bool ok, uint32_t (&
 // c_i = 2^(2^i - 127).  fma(weight, that, acc) therefore IS the bit-selected add, scaled by c_i; the
 // scale is exact (no product leaves the normal range, see kScaleLog2) and is removed once, after the
 // last key.  Two channels share one f32x2 FMA.  Measured on B200, this form beats per-bit predicated
-// adds: 47 us against 68-73 us per call at 64 sequences x [128, 4096] keys.
+// adds (47 us against 68-73 us per call at 64 sequences x [128, 4096] keys) and scalar FMAs on the
+// same masks (51 us against 60 us).
+typedef uint64_t AccT;    // two channels per f32x2 accumulator
+constexpr int kAccPerLane = 4;
+
 template <int W, int R>
-__device__ __forceinline__ void phase_b(const uint32_t* stage, int grp, int ls, uint64_t (&acc)[R][4]) {
+__device__ __forceinline__ void phase_b(const uint32_t* stage, int grp, int ls, AccT (&acc)[R][kAccPerLane]) {
     using M = Map<W>;
     using RW = Row<W, R>;
     const int word_off = RW::V_OFF + (ls >> 2);         // V word inside the staged row
@@ -215,7 +219,25 @@ attn_decode_kernel(const AttnParams p) {
     const int t = static_cast<int>(rest % p.T); rest /= p.T;
     const int gp = static_cast<int>(rest % (p.Hkv * p.passes)); rest /= (p.Hkv * p.passes);
     const int c = static_cast<int>(rest % p.splits); rest /= p.splits;
-    const int64_t n = rest;
+    int64_t n = rest;
+    if (p.n_seqs <= 128 && p.n_seqs > 1) {
+        // Longest rows first: this item serves the row whose length has rank `rest` (ties by index), so
+        // the long-running blocks are scheduled early and the last wave holds short ones.
+        const int want = static_cast<int>(rest);
+        int found = -1;
+        for (int j = lane; j < p.n_seqs; j += 32) {
+            const int lj = p.lens[j];
+            int rank = 0;
+            for (int i = 0; i < p.n_seqs; ++i) {
+                const int li = p.lens[i];
+                rank += (li > lj) || (li == lj && i < j);
+            }
+            if (rank == want) found = j;
+        }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) found = max(found, __shfl_xor_sync(0xffffffffu, found, o));
+        n = found;
+    }
     const int g = gp / p.passes;
     const int pass = gp - g * p.passes;
     const int h0 = g * p.n_rep + pass * R;
@@ -250,13 +272,13 @@ attn_decode_kernel(const AttnParams p) {
             cmax[hh] += __popc(qw[hh][w]);
         }
     }
-    uint64_t acc[R][4];
+    AccT acc[R][kAccPerLane];
     float lsum[R];
 #pragma unroll
     for (int hh = 0; hh < R; ++hh) {
         lsum[hh] = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[hh][i] = 0ull;
+        for (int i = 0; i < kAccPerLane; ++i) acc[hh][i] = 0;
     }
 
     const uint32_t* kbase = p.k + t * p.sk_t + g * p.sk_h;

@@ -19,25 +19,26 @@ __device__ __forceinline__ float clamp_beta(float b) {
 // One neuron's state across timesteps.
 struct Lif {
     float u;
-    bool fired;  // H(u - theta) of the current membrane
+    float rth;  // r * theta of the next step: theta if the current membrane is above threshold, else 0
+                // (1.0f * theta == theta and 0.0f * theta == 0 exactly for every finite theta, so the
+                // product is kept as a select; no predicate has to live across steps)
 
     __device__ __forceinline__ void init(float u0, float th) {
         u = u0;
-        fired = __fsub_rn(u, th) > 0.0f;
+        rth = __fsub_rn(u, th) > 0.0f ? th : 0.0f;
     }
     // Advances one step and returns the spike.
     template <int MODE>
     __device__ __forceinline__ bool step(float cur, float beta, float th) {
         if (MODE == SPK_RESET_SUBTRACT_DELAYED) {
-            const float r = fired ? 1.0f : 0.0f;
-            u = __fsub_rn(__fadd_rn(__fmul_rn(beta, u), cur), __fmul_rn(r, th));
-            fired = __fsub_rn(u, th) > 0.0f;
-            return fired;
+            u = __fsub_rn(__fadd_rn(__fmul_rn(beta, u), cur), rth);
+            const bool s = __fsub_rn(u, th) > 0.0f;
+            rth = s ? th : 0.0f;
+            return s;
         } else {
             u = __fadd_rn(__fmul_rn(beta, u), cur);
             const bool s = __fsub_rn(u, th) > 0.0f;
             if (s) u = 0.0f;
-            fired = false;
             return s;
         }
     }
