@@ -457,6 +457,97 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_tp7b(args) -> None:
+    """Secondary workload (BASELINE config 5): spiking Qwen2.5-7B shape (28 layers, hidden 3584, 28/4 heads,
+    head_dim 128, MLP 18944, vocab 152064, T=4, bf16), 256 concurrent decode sequences per replica with ragged
+    contexts log-uniform in [1k, 32k], head-sharded tensor parallel over min(N, 4) GPUs (NCCL all-reduce after
+    o_proj and down_proj), N/4 replicas beyond that.  The pools are filled with random bits and the batch state
+    is installed directly instead of prefilling 2.3 M tokens; every timed step is a full decode step."""
+    import math
+
+    import torch.distributed as dist
+
+    from spikeinfer_b200 import _lib
+    from spikeinfer_b200.engine.decode_engine import SpikeDecodeEngine
+    from spikeinfer_b200.engine.replicas import max_over_ranks
+    from spikeinfer_b200.modeling import SpikingQwenConfig, SpikingQwenModel
+    from spikeinfer_b200.tensor_parallel import shard_config
+
+    rank, world, local = dist_info()
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    tp = min(world, 4)
+    if world % tp:
+        raise SystemExit("world size must be 1, 2, 4 or a multiple of 4")
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        for g in range(world // tp):  # every rank creates every group, in the same order
+            pg = dist.new_group(list(range(g * tp, (g + 1) * tp)))
+            if rank // tp == g:
+                group = pg
+    cfg = SpikingQwenConfig(vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
+                            num_attention_heads=28, num_key_value_heads=4, head_dim=128)
+    lcfg = shard_config(cfg, tp)
+    weights = random_weights_device(lcfg, device, torch.bfloat16, seed=100 + rank // tp)  # replicated parts differ per
+    model = SpikingQwenModel(lcfg, weights, device=device, tp_group=group if tp > 1 else None)  # rank: irrelevant for timing
+    del weights
+    n_seq = args.tp_seqs
+    g = torch.Generator(device="cpu").manual_seed(5 + rank // tp)
+    lo, hi = math.log(1024.0), math.log(32768.0)
+    ctx = torch.exp(torch.rand(n_seq, generator=g) * (hi - lo) + lo).long().clamp(1024, 32768).tolist()
+    K, W = args.steps, max(args.warmup, 3)
+    max_len = 32768 + 2 * (K + W) + 64
+    blocks = sum(-(-(c + 2 * (K + W) + 16) // BLOCK_SIZE) for c in ctx) + 1
+    engine = SpikeDecodeEngine(model, num_blocks=blocks, block_size=BLOCK_SIZE, max_num_seqs=n_seq, max_model_len=max_len)
+    for k, v in engine.cache.layers:  # ~12.5 % set bits everywhere
+        for pool in (k, v):
+            r = torch.randint(-2**31, 2**31 - 1, (3, *pool.shape), dtype=torch.int32, device=device)
+            pool.copy_(r[0] & r[1] & r[2])
+            del r
+    for row, c in enumerate(ctx):
+        table = engine.state.take_blocks(-(-c // BLOCK_SIZE))
+        engine.state.admit(row, table, c, row % cfg.vocab_size)
+    engine.free_rows = []
+    lib = _lib.load()
+    before = lib.spk_launch_count()
+    engine.capture()
+    launches_per_step = (lib.spk_launch_count() - before) // 4
+    torch.cuda.synchronize(device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(W):
+        engine.decode_step()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local) as clocks:
+        start.record()
+        for _ in range(K):
+            engine.decode_step()
+        stop.record()
+        barrier()
+    engine.state.check_status()
+    (ms,) = max_over_ranks([start.elapsed_time(stop)], device)
+    sum_ctx = sum(ctx)
+    if rank == 0:
+        kv_bytes = sum_ctx * lcfg.T * lcfg.num_key_value_heads * 2 * 4 * 4  # K+V words of one layer on one GPU
+        print(json.dumps({
+            "workload": "tp7b_256seq_longctx", "metric": "decode_tok_per_s_7B_spiking_T4", "unit": UNIT,
+            "value": round(n_seq * (world // tp) * K / (ms * 1e-3), 1), "n_gpus": world, "tensor_parallel": tp,
+            "replicas": world // tp, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 3), "dtype": "bf16",
+            "data": "synthetic (pools pre-filled with random bits, no prefill)", "sequences_per_replica": n_seq,
+            "sum_context_tokens": sum_ctx, "attention_kv_bytes_per_layer_per_gpu": kv_bytes,
+            "all_reduce_bytes_per_call": lcfg.T * n_seq * cfg.hidden_size * 2, "all_reduces_per_step": 2 * cfg.num_hidden_layers if tp > 1 else 0,
+            "gpu_launches_per_step": launches_per_step, "clocks": clocks.summary()}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -470,8 +561,13 @@ def main() -> None:
                     help="time only the kernel-level configuration of the attention or the LIF kernel")
     ap.add_argument("--pools", type=int, default=24, help="distinct K/V pools of --kernel-bench attn")
     ap.add_argument("--tokens", type=int, default=8192, help="tokens of --kernel-bench lif")
+    ap.add_argument("--workload", choices=["decode_0p5b", "tp7b"], default="decode_0p5b",
+                    help="tp7b: the 7B-shape long-context tensor-parallel decode step (secondary line)")
+    ap.add_argument("--tp-seqs", type=int, default=256, help="sequences per replica of --workload tp7b")
     args = ap.parse_args()
-    if args.kernel_bench:
+    if args.workload == "tp7b" and args.impl == "own" and not args.kernel_bench:
+        run_tp7b(args)
+    elif args.kernel_bench:
         run_kernel_bench(args)
     elif args.impl == "reference":
         run_reference(args)

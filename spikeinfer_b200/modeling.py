@@ -73,8 +73,12 @@ class SpikingQwenModel:
     """Inference-only model over a weights dict; every tensor lives on ``device``."""
 
     def __init__(self, config: SpikingQwenConfig, weights: dict, device: str | torch.device = "cuda",
-                 dtype: torch.dtype | None = None) -> None:
+                 dtype: torch.dtype | None = None, tp_group=None) -> None:
+        """``tp_group``: a ``torch.distributed`` process group when ``config``/``weights`` are one rank's shard
+        of a head-sharded model (see :mod:`spikeinfer_b200.tensor_parallel`); the partial outputs of
+        ``o_proj`` and ``down_proj`` are then summed over the group."""
         self.config = config
+        self.tp_group = tp_group
         self.device = torch.device(device)
         _lib.require_cuda(torch.empty(0, device=self.device), "SpikingQwenModel device")
         c = config
@@ -113,6 +117,12 @@ class SpikingQwenModel:
                                      f"(min={th.min().item():.4g})")
         return True
 
+    def _reduce(self, partial: torch.Tensor) -> torch.Tensor:
+        """Sum a row-sharded projection's partial outputs over the tensor-parallel group (NCCL all-reduce)."""
+        if self.tp_group is not None:
+            torch.distributed.all_reduce(partial, group=self.tp_group)
+        return partial
+
     def rope(self, positions: torch.Tensor):
         freqs = positions.to(torch.float32)[:, None] * self.inv_freq[None, :]
         emb = torch.cat((freqs, freqs), dim=-1)
@@ -135,11 +145,11 @@ class SpikingQwenModel:
             qkv = F.linear(x, L["w_qkv"], L["b_qkv"])  # [T, n_tok, (hq + 2 hkv) d]
             ctx = fused_qkv_attention(qkv, L["lif_q"], L["lif_k"], L["lif_v"], kv_caches[i][0], kv_caches[i][1],
                                       meta, hq, hkv, d, rope=rope)
-            delta = F.linear(ctx, L["w_o"])
+            delta = self._reduce(F.linear(ctx, L["w_o"]))
             x = add_rms_norm(h, delta, L["ln2"], c.rms_norm_eps)
             gu = F.linear(x, L["w_gate_up"])  # [T, n_tok, 2 * inter]
             act = lif_gate_mul(gu[..., : c.intermediate_size], gu[..., c.intermediate_size:], *L["lif_gate"])
-            delta = F.linear(act, L["w_down"])
+            delta = self._reduce(F.linear(act, L["w_down"]))
         return add_rms_norm(h, delta, self.norm, c.rms_norm_eps).mean(dim=0)
 
     @torch.no_grad()
