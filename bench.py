@@ -473,25 +473,42 @@ def run_tp7b(args) -> None:
     from spikeinfer_b200.modeling import SpikingQwenConfig, SpikingQwenModel
     from spikeinfer_b200.tensor_parallel import shard_config
 
+    # In-switch reduction (NVLS) is left off: the all-reduce is captured in a CUDA graph here and a rank that
+    # exits while bound to an NVLink multicast object can disturb its peers on shared machines.
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     rank, world, local = dist_info()
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
+
+    def stage(msg):
+        if args.verbose:
+            print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
+
     tp = min(world, 4)
     if world % tp:
         raise SystemExit("world size must be 1, 2, 4 or a multiple of 4")
     group = None
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-        for g in range(world // tp):  # every rank creates every group, in the same order
-            pg = dist.new_group(list(range(g * tp, (g + 1) * tp)))
-            if rank // tp == g:
-                group = pg
+        if world == tp:
+            group = dist.group.WORLD
+        else:
+            for g in range(world // tp):  # every rank creates every group, in the same order
+                pg = dist.new_group(list(range(g * tp, (g + 1) * tp)))
+                if rank // tp == g:
+                    group = pg
     cfg = SpikingQwenConfig(vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
                             num_attention_heads=28, num_key_value_heads=4, head_dim=128)
     lcfg = shard_config(cfg, tp)
     weights = random_weights_device(lcfg, device, torch.bfloat16, seed=100 + rank // tp)  # replicated parts differ per
     model = SpikingQwenModel(lcfg, weights, device=device, tp_group=group if tp > 1 else None)  # rank: irrelevant for timing
     del weights
+    stage("model built")
+    if tp > 1:  # first collective of the group outside any capture: communicator set-up happens here
+        probe = torch.ones(1, device=device)
+        dist.all_reduce(probe, group=group)
+        torch.cuda.synchronize(device)
+        stage(f"group all-reduce ok ({probe.item():.0f})")
     n_seq = args.tp_seqs
     g = torch.Generator(device="cpu").manual_seed(5 + rank // tp)
     lo, hi = math.log(1024.0), math.log(32768.0)
@@ -509,11 +526,14 @@ def run_tp7b(args) -> None:
         table = engine.state.take_blocks(-(-c // BLOCK_SIZE))
         engine.state.admit(row, table, c, row % cfg.vocab_size)
     engine.free_rows = []
+    torch.cuda.synchronize(device)
+    stage("pools filled, rows admitted")
     lib = _lib.load()
     before = lib.spk_launch_count()
     engine.capture()
     launches_per_step = (lib.spk_launch_count() - before) // 4
     torch.cuda.synchronize(device)
+    stage("decode graph captured")
 
     def barrier():
         if world > 1:
@@ -522,14 +542,18 @@ def run_tp7b(args) -> None:
 
     for _ in range(W):
         engine.decode_step()
+    torch.cuda.synchronize(device)
+    stage("warm-up replays done")
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    stage("barrier passed")
     with ClockSampler(local) as clocks:
         start.record()
         for _ in range(K):
             engine.decode_step()
         stop.record()
         barrier()
+    stage("timed steps done")
     engine.state.check_status()
     (ms,) = max_over_ranks([start.elapsed_time(stop)], device)
     sum_ctx = sum(ctx)
@@ -544,7 +568,15 @@ def run_tp7b(args) -> None:
             "all_reduce_bytes_per_call": lcfg.T * n_seq * cfg.hidden_size * 2, "all_reduces_per_step": 2 * cfg.num_hidden_layers if tp > 1 else 0,
             "gpu_launches_per_step": launches_per_step, "clocks": clocks.summary()}), flush=True)
     if world > 1:
+        # the captured graph holds the communicator's kernels: release it before the group is torn down
+        import gc
+
         dist.barrier()
+        torch.cuda.synchronize(device)
+        engine.graph = None
+        del engine, model
+        gc.collect()
+        torch.cuda.synchronize(device)
         dist.destroy_process_group()
 
 
@@ -564,6 +596,7 @@ def main() -> None:
     ap.add_argument("--workload", choices=["decode_0p5b", "tp7b"], default="decode_0p5b",
                     help="tp7b: the 7B-shape long-context tensor-parallel decode step (secondary line)")
     ap.add_argument("--tp-seqs", type=int, default=256, help="sequences per replica of --workload tp7b")
+    ap.add_argument("--verbose", action="store_true", help="print progress of the set-up stages to stderr")
     args = ap.parse_args()
     if args.workload == "tp7b" and args.impl == "own" and not args.kernel_bench:
         run_tp7b(args)
