@@ -5,8 +5,8 @@
 // reference): the membrane is fp32 whatever the input type; beta is clamped to
 // [0,1]; every step is ((beta*u) + I) - (r*theta) with each mul/add/sub rounded
 // on its own (no FMA contraction: the __f*_rn intrinsics are never fused); the
-// reset r is taken from the previous membrane; a spike is (u - theta) > 0, not
-// u > theta.
+// reset r is taken from the previous membrane; a spike is (u - theta) > 0 (see the
+// note at struct Lif on why comparing u > theta directly is the same predicate here).
 #include "spk_common.cuh"
 
 namespace {
@@ -17,30 +17,51 @@ __device__ __forceinline__ float clamp_beta(float b) {
 }
 
 // One neuron's state across timesteps.
+//
+// The spike predicate of the reference is (u - theta) > 0.  In IEEE arithmetic without flush-to-zero (this
+// library is built without -ftz) a difference rounds to zero only when its operands are equal, and it is NaN
+// exactly when the comparison is unordered, so (u - theta) > 0 and u > theta are the same predicate; the
+// step below therefore compares directly and saves the subtraction.  The reset term r * theta is kept as
+// "theta or 0" (1.0f * theta == theta and 0.0f * theta == 0 exactly for every finite theta).  The step is
+// written in PTX so that the predicate is consumed by the next two instructions: with 8 channels in flight
+// per lane, longer-lived predicates overflow the 7 predicate registers and cost a select + compare each.
 struct Lif {
     float u;
-    float rth;  // r * theta of the next step: theta if the current membrane is above threshold, else 0
-                // (1.0f * theta == theta and 0.0f * theta == 0 exactly for every finite theta, so the
-                // product is kept as a select; no predicate has to live across steps)
+    float rth;
 
     __device__ __forceinline__ void init(float u0, float th) {
         u = u0;
-        rth = __fsub_rn(u, th) > 0.0f ? th : 0.0f;
+        rth = u > th ? th : 0.0f;
     }
-    // Advances one step and returns the spike.
+    // Advances one step; ORs `bit` into `bits` when the neuron spikes.
+    template <int MODE>
+    __device__ __forceinline__ void step(float cur, float beta, float th, uint32_t bit, uint32_t& bits) {
+        if (MODE == SPK_RESET_SUBTRACT_DELAYED) {
+            asm("{\n\t.reg .pred p;\n\t"
+                "mul.rn.f32 %0, %3, %0;\n\t"
+                "add.rn.f32 %0, %0, %4;\n\t"
+                "sub.rn.f32 %0, %0, %1;\n\t"
+                "setp.gt.f32 p, %0, %5;\n\t"
+                "selp.f32 %1, %5, 0f00000000, p;\n\t"
+                "@p or.b32 %2, %2, %6;\n\t}"
+                : "+f"(u), "+f"(rth), "+r"(bits)
+                : "f"(beta), "f"(cur), "f"(th), "r"(bit));
+        } else {
+            asm("{\n\t.reg .pred p;\n\t"
+                "mul.rn.f32 %0, %2, %0;\n\t"
+                "add.rn.f32 %0, %0, %3;\n\t"
+                "setp.gt.f32 p, %0, %4;\n\t"
+                "@p mov.f32 %0, 0f00000000;\n\t"
+                "@p or.b32 %1, %1, %5;\n\t}"
+                : "+f"(u), "+r"(bits)
+                : "f"(beta), "f"(cur), "f"(th), "r"(bit));
+        }
+    }
     template <int MODE>
     __device__ __forceinline__ bool step(float cur, float beta, float th) {
-        if (MODE == SPK_RESET_SUBTRACT_DELAYED) {
-            u = __fsub_rn(__fadd_rn(__fmul_rn(beta, u), cur), rth);
-            const bool s = __fsub_rn(u, th) > 0.0f;
-            rth = s ? th : 0.0f;
-            return s;
-        } else {
-            u = __fadd_rn(__fmul_rn(beta, u), cur);
-            const bool s = __fsub_rn(u, th) > 0.0f;
-            if (s) u = 0.0f;
-            return s;
-        }
+        uint32_t b = 0;
+        step<MODE>(cur, beta, th, 1u, b);
+        return b != 0;
     }
 };
 
@@ -117,6 +138,10 @@ struct Raw8<float> {
         a = __ldg(reinterpret_cast<const float4*>(p));
         b = __ldg(reinterpret_cast<const float4*>(p) + 1);
     }
+    __device__ __forceinline__ void from_smem(const uint4* p) {  // two pieces, 32 lanes apart
+        a = *reinterpret_cast<const float4*>(p);
+        b = *reinterpret_cast<const float4*>(p + 32);
+    }
     __device__ __forceinline__ void clear() { a = make_float4(0, 0, 0, 0); b = a; }
     __device__ __forceinline__ float get(int i) const {
         switch (i) {
@@ -129,6 +154,7 @@ template <>
 struct Raw8<__nv_bfloat16> {
     uint4 v;
     __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = __ldg(reinterpret_cast<const uint4*>(p)); }
+    __device__ __forceinline__ void from_smem(const uint4* p) { v = *p; }
     __device__ __forceinline__ void clear() { v = make_uint4(0, 0, 0, 0); }
     __device__ __forceinline__ float get(int i) const {
         const uint32_t w = (i >> 1) == 0 ? v.x : (i >> 1) == 1 ? v.y : (i >> 1) == 2 ? v.z : v.w;
@@ -140,6 +166,7 @@ template <>
 struct Raw8<__half> {
     uint4 v;
     __device__ __forceinline__ void load(const __half* p) { v = __ldg(reinterpret_cast<const uint4*>(p)); }
+    __device__ __forceinline__ void from_smem(const uint4* p) { v = *p; }
     __device__ __forceinline__ void clear() { v = make_uint4(0, 0, 0, 0); }
     __device__ __forceinline__ float get(int i) const {
         const uint32_t w = (i >> 1) == 0 ? v.x : (i >> 1) == 1 ? v.y : (i >> 1) == 2 ? v.z : v.w;
@@ -214,12 +241,27 @@ struct VecArgs {
     uint32_t per_tok[SPK_MAX_LIF_SITES];  // segments per token = H * per_row
     uint32_t per_row[SPK_MAX_LIF_SITES];  // segments per (token, head) row = N / 8
     int32_t toks;                          // consecutive tokens a lane walks (amortises the parameter loads)
+    int32_t slots;                         // 16-byte slots per lane and stage in the streaming form
 };
 
-template <typename TX, int MODE, bool ROPE>
+// Asynchronous 16-byte global -> shared copy (per-thread completion groups).
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem))), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int kStages = 3;  // tokens in flight per lane in the streaming form
+
+// ASYNC (the streaming form for bandwidth-sized launches): a lane walks `toks` tokens and keeps the
+// currents (and multiplicands) of the next kStages-1 tokens in flight with cp.async into its own slots
+// of shared memory, so the bytes in flight per SM no longer depend on how many registers a warp holds.
+// Every lane reads back only what it copied itself, so no barrier is involved.  Needs T <= 4, no RoPE.
+template <typename TX, int MODE, bool ROPE, bool FULL, bool ASYNC>
 __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t units, uint32_t per_tok,
                                                uint32_t per_row, int toks, uint32_t unit, int lane, int T,
-                                               int64_t n_tok, uint32_t* status) {
+                                               int64_t n_tok, uint32_t* status, uint4* stage, int slots) {
     // 32-bit index arithmetic only: one lane = (token group, head, 8-channel segment)
     const bool in_range = unit < units;
     const uint32_t u_ = in_range ? unit : 0u;
@@ -250,16 +292,59 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
     const int64_t partner_off = first_half ? s.N / 2 : -(s.N / 2);
     const float partner_sign = first_half ? -1.0f : 1.0f;
 
+    // Site fields used in the loops, read once.
+    const int64_t sx_t = s.sx_t, so_t = s.so_t, sd_t = s.sd_t, sm_t = s.sm_t, sg_t = s.sg_t, N = s.N;
+    const bool has_packed = s.packed != nullptr, has_dense = s.dense != nullptr, has_gated = s.gated != nullptr;
+    const unsigned group_mask = 0xFu << (lane & 28);  // the four lanes that build one word together
+
+    constexpr int VECS = sizeof(TX) * kSeg / 16;  // 16-byte pieces of one 8-channel segment
+    auto issue = [&](int jj) {
+        const int64_t tk = static_cast<int64_t>(grp) * toks + jj;
+        if (jj < toks && in_range && tk < n_tok) {
+            uint4* dst = stage + (jj % kStages) * slots * 32;
+            const TX* xj = static_cast<const TX*>(s.x) + tk * s.sx_tok + static_cast<int64_t>(h) * s.sx_h + c0;
+#pragma unroll
+            for (int i = 0; i < kStepGroup; ++i) {
+                if (FULL || i < T) {
+#pragma unroll
+                    for (int v = 0; v < VECS; ++v) cp_async16(dst + (i * VECS + v) * 32, xj + i * sx_t + v * (16 / sizeof(TX)));
+                }
+            }
+            if (has_gated) {
+                const TX* mj = static_cast<const TX*>(s.mul) + tk * s.sm_tok + static_cast<int64_t>(h) * s.sm_h + c0;
+#pragma unroll
+                for (int i = 0; i < kStepGroup; ++i) {
+                    if (FULL || i < T) {
+#pragma unroll
+                        for (int v = 0; v < VECS; ++v)
+                            cp_async16(dst + ((kStepGroup + i) * VECS + v) * 32, mj + i * sm_t + v * (16 / sizeof(TX)));
+                    }
+                }
+            }
+        }
+        cp_async_commit();
+    };
+    if (ASYNC) {
+#pragma unroll
+        for (int jj = 0; jj < kStages - 1; ++jj) issue(jj);
+    }
+
     for (int j = 0; j < toks; ++j) {
         const int64_t tok = static_cast<int64_t>(grp) * toks + j;
-        const bool live = in_range && tok < n_tok;
+        if (ASYNC) {
+            issue(j + kStages - 1);
+            cp_async_wait<kStages - 1>();  // this lane's copies for token j have landed
+        }
+        // The four lanes of a word share (token group, head, word), so they are live or dead together and a
+        // dead group can skip the token entirely (the shuffles below only involve its own four lanes).
+        if (!(in_range && tok < n_tok)) continue;
         const int64_t row = tok * s.H + h;
         Lif st[kSeg];
         {
             float u0[kSeg] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (live && s.mem0 != nullptr) {
-                const float4 m0 = __ldg(reinterpret_cast<const float4*>(s.mem0 + row * s.N + c0));
-                const float4 m1 = __ldg(reinterpret_cast<const float4*>(s.mem0 + row * s.N + c0) + 1);
+            if (s.mem0 != nullptr) {
+                const float4 m0 = __ldg(reinterpret_cast<const float4*>(s.mem0 + row * N + c0));
+                const float4 m1 = __ldg(reinterpret_cast<const float4*>(s.mem0 + row * N + c0) + 1);
                 u0[0] = m0.x; u0[1] = m0.y; u0[2] = m0.z; u0[3] = m0.w;
                 u0[4] = m1.x; u0[5] = m1.y; u0[6] = m1.z; u0[7] = m1.w;
             }
@@ -267,48 +352,77 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
             for (int i = 0; i < kSeg; ++i) st[i].init(u0[i], th[i]);
         }
         int64_t out_row = tok;
-        bool row_ok = live;
-        if (live && s.packed != nullptr && s.slot_mapping != nullptr) {
+        bool row_ok = true;
+        if (has_packed && s.slot_mapping != nullptr) {
             out_row = s.slot_mapping[tok];
             row_ok = out_row >= 0 && out_row < s.num_rows;
             if (!row_ok && sg == 0) spk_flag(status, SPK_STATUS_BAD_SLOT);
         }
-        const TX* xp = static_cast<const TX*>(s.x) + tok * s.sx_tok + static_cast<int64_t>(h) * s.sx_h + c0;
+        const int64_t head = static_cast<int64_t>(h);
+        const TX* xp = static_cast<const TX*>(s.x) + tok * s.sx_tok + head * s.sx_h + c0;
+        const TX* mp = has_gated ? static_cast<const TX*>(s.mul) + tok * s.sm_tok + head * s.sm_h + c0 : nullptr;
+        TX* gp = has_gated ? static_cast<TX*>(s.gated) + tok * s.sg_tok + head * s.sg_h + c0 : nullptr;
+        int64_t dense_idx = tok * s.sd_tok + head * s.sd_h + c0;
+        uint32_t* wp = has_packed && row_ok
+            ? reinterpret_cast<uint32_t*>(s.packed) + out_row * s.so_tok + head * s.so_h + (sg >> 2) + sub * so_t
+            : nullptr;
         float rc[kSeg], rs[kSeg];
         if (rope) {
             Raw8<TX> cr, sr;
-            if (live) {
-                cr.load(static_cast<const TX*>(s.rope_cos) + tok * s.s_rope_tok + c0);
-                sr.load(static_cast<const TX*>(s.rope_sin) + tok * s.s_rope_tok + c0);
-            } else {
-                cr.clear();
-                sr.clear();
-            }
+            cr.load(static_cast<const TX*>(s.rope_cos) + tok * s.s_rope_tok + c0);
+            sr.load(static_cast<const TX*>(s.rope_sin) + tok * s.s_rope_tok + c0);
 #pragma unroll
             for (int c = 0; c < kSeg; ++c) { rc[c] = cr.get(c); rs[c] = sr.get(c); }
         }
 
+        if (ASYNC) {
+            // Streaming form: one timestep at a time straight from this lane's shared-memory slots (T <= 4),
+            // rolled loop: few live registers, small code.
+            const uint4* mine_stage = stage + (j % kStages) * slots * 32;
+            uint32_t mine = 0;
+#pragma unroll 1
+            for (int i = 0; i < kStepGroup; ++i) {
+                uint32_t bits = 0;
+                if (FULL || i < T) {
+                    Raw8<TX> raw;
+                    raw.from_smem(mine_stage + i * VECS * 32);
+#pragma unroll
+                    for (int c = 0; c < kSeg; ++c) st[c].template step<MODE>(raw.get(c), b[c], th[c], 1u << c, bits);
+                    if (has_gated) {
+                        Raw8<TX> m;
+                        m.from_smem(mine_stage + (kStepGroup + i) * VECS * 32);
+                        float g[kSeg];
+#pragma unroll
+                        for (int c = 0; c < kSeg; ++c) g[c] = (bits >> c) & 1u ? m.get(c) : 0.0f;
+                        store8<TX>(gp + i * sg_t, g);
+                    }
+                    if (has_dense) store_dense8(s.dense, s.dense_dtype, dense_idx + i * sd_t, bits);
+                }
+                uint32_t word = bits << (8 * sub);
+                word |= __shfl_xor_sync(group_mask, word, 1);
+                word |= __shfl_xor_sync(group_mask, word, 2);
+                if (sub == i) mine = word;
+            }
+            if (wp != nullptr && (FULL || sub < T)) *wp = mine;
+        } else
         for (int t0 = 0; t0 < T; t0 += kStepGroup) {
             Raw8<TX> raw[kStepGroup], partner[kStepGroup], mulv[kStepGroup];
-            const bool gated = live && s.gated != nullptr;
 #pragma unroll
             for (int i = 0; i < kStepGroup; ++i) {
-                if (live && t0 + i < T) raw[i].load(xp + (t0 + i) * s.sx_t);
-                else raw[i].clear();
-                if (gated && t0 + i < T)
-                    mulv[i].load(static_cast<const TX*>(s.mul) + (t0 + i) * s.sm_t + tok * s.sm_tok +
-                                 static_cast<int64_t>(h) * s.sm_h + c0);
-                else mulv[i].clear();
+                const bool on = FULL || t0 + i < T;
+                if (!FULL) { raw[i].clear(); mulv[i].clear(); }
+                if (on) raw[i].load(xp + i * sx_t);
+                if (has_gated && on) mulv[i].load(mp + i * sm_t);
                 if (rope) {
-                    if (live && t0 + i < T) partner[i].load(xp + (t0 + i) * s.sx_t + partner_off);
-                    else partner[i].clear();
+                    if (!FULL) partner[i].clear();
+                    if (on) partner[i].load(xp + i * sx_t + partner_off);
                 }
             }
             uint32_t mine = 0;
 #pragma unroll
             for (int i = 0; i < kStepGroup; ++i) {
                 uint32_t bits = 0;
-                if (t0 + i < T) {
+                if (FULL || t0 + i < T) {
 #pragma unroll
                     for (int c = 0; c < kSeg; ++c) {
                         float cur = raw[i].get(c);
@@ -318,60 +432,55 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
                             const float r = round_to<TX>(__fmul_rn(partner_sign * partner[i].get(c), rs[c]));
                             cur = round_to<TX>(__fadd_rn(a, r));
                         }
-                        bits |= st[c].template step<MODE>(cur, b[c], th[c]) ? (1u << c) : 0u;
+                        st[c].template step<MODE>(cur, b[c], th[c], 1u << c, bits);
                     }
-                    if (!live) bits = 0;
-                    if (gated) {
+                    if (has_gated) {
                         // gated[t, tok, h, c] = spike ? mul[t, tok, h, c] : 0   (the spike * up product)
                         float g[kSeg];
 #pragma unroll
                         for (int c = 0; c < kSeg; ++c) g[c] = (bits >> c) & 1u ? mulv[i].get(c) : 0.0f;
-                        store8<TX>(static_cast<TX*>(s.gated) + (t0 + i) * s.sg_t + tok * s.sg_tok +
-                                   static_cast<int64_t>(h) * s.sg_h + c0, g);
+                        store8<TX>(gp + i * sg_t, g);
                     }
-                    if (live && s.dense != nullptr)
-                        store_dense8(s.dense, s.dense_dtype,
-                                     (t0 + i) * s.sd_t + tok * s.sd_tok + static_cast<int64_t>(h) * s.sd_h + c0, bits);
+                    if (has_dense) store_dense8(s.dense, s.dense_dtype, dense_idx + (t0 + i) * sd_t, bits);
                 }
                 uint32_t word = bits << (8 * sub);
-                word |= __shfl_xor_sync(0xffffffffu, word, 1);
-                word |= __shfl_xor_sync(0xffffffffu, word, 2);
+                word |= __shfl_xor_sync(group_mask, word, 1);
+                word |= __shfl_xor_sync(group_mask, word, 2);
                 if (sub == i) mine = word;
             }
-            if (s.packed != nullptr && row_ok && t0 + sub < T)
-                reinterpret_cast<uint32_t*>(s.packed)[(t0 + sub) * s.so_t + out_row * s.so_tok +
-                                                      static_cast<int64_t>(h) * s.so_h + (sg >> 2)] = mine;
+            if (wp != nullptr && (FULL || t0 + sub < T)) *wp = mine;
+            xp += kStepGroup * sx_t;
+            if (has_gated) { mp += kStepGroup * sm_t; gp += kStepGroup * sg_t; }
+            if (wp != nullptr) wp += kStepGroup * so_t;
         }
-        if (live && s.mem_out != nullptr) {
-            float4* o = reinterpret_cast<float4*>(s.mem_out + row * s.N + c0);
+        if (s.mem_out != nullptr) {
+            float4* o = reinterpret_cast<float4*>(s.mem_out + row * N + c0);
             o[0] = make_float4(st[0].u, st[1].u, st[2].u, st[3].u);
             o[1] = make_float4(st[4].u, st[5].u, st[6].u, st[7].u);
         }
     }
 }
 
-template <int MODE, bool ROPE>
-__global__ void __launch_bounds__(kFusedThreads)
+template <int MODE, bool ROPE, bool FULL, bool ASYNC>
+__global__ void __launch_bounds__(kFusedThreads, ROPE ? 1 : (ASYNC ? 4 : 2))
 lif_pack_scatter_vec_kernel(VecArgs args, int T, int64_t n_tok, uint32_t* status) {
+    extern __shared__ uint4 stage_smem[];
     const int site = blockIdx.y;
     const int lane = threadIdx.x & 31;
     const uint32_t unit = blockIdx.x * kFusedThreads + threadIdx.x;
     if (unit - lane >= args.units[site]) return;  // whole warp out of range
     const spk_lif_site& s = args.s[site];
+    // this lane's slots: [warp][stage][slot][lane]
+    uint4* stage = ASYNC ? stage_smem + (threadIdx.x >> 5) * kStages * args.slots * 32 + lane : nullptr;
+#define SPK_SITE(TX_) \
+    fused_site_vec<TX_, MODE, ROPE, FULL, ASYNC>(s, args.units[site], args.per_tok[site], args.per_row[site], \
+                                                 args.toks, unit, lane, T, n_tok, status, stage, args.slots)
     switch (s.x_dtype) {
-        case SPK_F32:
-            fused_site_vec<float, MODE, ROPE>(s, args.units[site], args.per_tok[site], args.per_row[site], args.toks,
-                                        unit, lane, T, n_tok, status);
-            break;
-        case SPK_BF16:
-            fused_site_vec<__nv_bfloat16, MODE, ROPE>(s, args.units[site], args.per_tok[site], args.per_row[site],
-                                                args.toks, unit, lane, T, n_tok, status);
-            break;
-        default:
-            fused_site_vec<__half, MODE, ROPE>(s, args.units[site], args.per_tok[site], args.per_row[site], args.toks,
-                                         unit, lane, T, n_tok, status);
-            break;
+        case SPK_F32: SPK_SITE(float); break;
+        case SPK_BF16: SPK_SITE(__nv_bfloat16); break;
+        default: SPK_SITE(__half); break;
     }
+#undef SPK_SITE
 }
 
 static inline bool is_aligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; }
@@ -603,9 +712,20 @@ extern "C" int spk_lif_pack_scatter(const spk_lif_site* sites, int n_sites, int 
         // tokens per lane: 4 once that still leaves every SM a few thousand lanes, else 2 or 1
         int64_t widest = 0;
         for (int i = 0; i < n_sites; ++i) widest = widest > sites[i].H * (sites[i].N / kSeg) ? widest : sites[i].H * (sites[i].N / kSeg);
+        bool any_rope = false, any_gated = false, any_f32 = false;
+        for (int i = 0; i < n_sites; ++i) {
+            any_rope = any_rope || sites[i].rope_cos != nullptr;
+            any_gated = any_gated || sites[i].gated != nullptr;
+            any_f32 = any_f32 || sites[i].x_dtype == SPK_F32;
+        }
         int toks = 4;
         while (toks > 1 && (n_tok / toks) * widest < 148LL * 2048) toks >>= 1;
+        // Bandwidth-sized launches stream through shared memory (cp.async, kStages tokens in flight per lane).
+        const bool streaming = !any_rope && T <= kStepGroup && toks == 4 && (n_tok / 8) * widest >= 148LL * 2048;
+        if (streaming) toks = 8;
         va.toks = toks;
+        va.slots = kStepGroup * (any_f32 ? 2 : 1) * (any_gated ? 2 : 1);
+        const size_t stage_bytes = streaming ? static_cast<size_t>(kFusedThreads / 32) * kStages * va.slots * 32 * 16 : 0;
         const int64_t groups = (n_tok + toks - 1) / toks;
         int64_t max_units = 0;
         for (int i = 0; i < SPK_MAX_LIF_SITES; ++i) {
@@ -629,17 +749,28 @@ extern "C" int spk_lif_pack_scatter(const spk_lif_site* sites, int n_sites, int 
             const int64_t vblocks = (max_units + kFusedThreads - 1) / kFusedThreads;
             dim3 vgrid(static_cast<unsigned>(vblocks), static_cast<unsigned>(n_sites));
             cudaStream_t vst = spk_stream(stream);
-            bool any_rope = false;
-            for (int i = 0; i < n_sites; ++i) any_rope = any_rope || sites[i].rope_cos != nullptr;
             const bool sub = reset_mode == SPK_RESET_SUBTRACT_DELAYED;
-            if (sub && any_rope)
-                lif_pack_scatter_vec_kernel<SPK_RESET_SUBTRACT_DELAYED, true><<<vgrid, kFusedThreads, 0, vst>>>(va, T, n_tok, status);
-            else if (sub)
-                lif_pack_scatter_vec_kernel<SPK_RESET_SUBTRACT_DELAYED, false><<<vgrid, kFusedThreads, 0, vst>>>(va, T, n_tok, status);
-            else if (any_rope)
-                lif_pack_scatter_vec_kernel<SPK_RESET_HARD_ZERO, true><<<vgrid, kFusedThreads, 0, vst>>>(va, T, n_tok, status);
-            else
-                lif_pack_scatter_vec_kernel<SPK_RESET_HARD_ZERO, false><<<vgrid, kFusedThreads, 0, vst>>>(va, T, n_tok, status);
+            const bool full = T % kStepGroup == 0;  // no partial group of timesteps: the per-step bounds checks drop out
+#define SPK_LAUNCH_VEC(MODE_, ROPE_, FULL_, ASYNC_)                                                                   \
+    do {                                                                                                              \
+        auto kern = lif_pack_scatter_vec_kernel<MODE_, ROPE_, FULL_, ASYNC_>;                                         \
+        if (stage_bytes > 48 * 1024) {                                                                                \
+            const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+                                                       static_cast<int>(stage_bytes));                                \
+            if (e != cudaSuccess) return spk_set_cuda_error(e);                                                       \
+        }                                                                                                             \
+        kern<<<vgrid, kFusedThreads, stage_bytes, vst>>>(va, T, n_tok, status);                                       \
+    } while (0)
+#define SPK_LAUNCH_MODE(MODE_)                                                          \
+    do {                                                                                \
+        if (streaming) { if (full) SPK_LAUNCH_VEC(MODE_, false, true, true); else SPK_LAUNCH_VEC(MODE_, false, false, true); } \
+        else if (any_rope) { if (full) SPK_LAUNCH_VEC(MODE_, true, true, false); else SPK_LAUNCH_VEC(MODE_, true, false, false); } \
+        else { if (full) SPK_LAUNCH_VEC(MODE_, false, true, false); else SPK_LAUNCH_VEC(MODE_, false, false, false); } \
+    } while (0)
+            if (sub) SPK_LAUNCH_MODE(SPK_RESET_SUBTRACT_DELAYED);
+            else SPK_LAUNCH_MODE(SPK_RESET_HARD_ZERO);
+#undef SPK_LAUNCH_MODE
+#undef SPK_LAUNCH_VEC
             SPK_CHECK_LAUNCH();
             return SPK_OK;
         }
