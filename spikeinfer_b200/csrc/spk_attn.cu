@@ -221,21 +221,42 @@ attn_decode_kernel(const AttnParams p) {
     const int c = static_cast<int>(rest % p.splits); rest /= p.splits;
     int64_t n = rest;
     if (p.n_seqs <= 128 && p.n_seqs > 1) {
-        // Longest rows first: this item serves the row whose length has rank `rest` (ties by index), so
-        // the long-running blocks are scheduled early and the last wave holds short ones.
-        const int want = static_cast<int>(rest);
-        int found = -1;
-        for (int j = lane; j < p.n_seqs; j += 32) {
-            const int lj = p.lens[j];
-            int rank = 0;
-            for (int i = 0; i < p.n_seqs; ++i) {
-                const int li = p.lens[i];
-                rank += (li > lj) || (li == lj && i < j);
-            }
-            if (rank == want) found = j;
-        }
+        // Longest rows first (coarsely): rows are ranked by length class (8 classes of max_keys / 8 keys),
+        // ties by index, and this item serves the row of rank `rest`.  The long-running CTAs are thus
+        // scheduled early and the last wave holds short rows.  Ballots over the lengths held one or a
+        // few per lane: a few dozen instructions per warp.
+        const int64_t max_keys_ = p.max_blocks << p.bs_log2;
+        int shift = 0;
+        while ((max_keys_ >> shift) > 8) ++shift;
+        int cls[4];
 #pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) found = max(found, __shfl_xor_sync(0xffffffffu, found, o));
+        for (int k = 0; k < 4; ++k) {
+            const int j = lane + 32 * k;
+            int v = -1;
+            if (j < p.n_seqs) {
+                const int lj = p.lens[j];
+                v = lj <= 0 ? 0 : min(7, (lj - 1) >> shift);
+            }
+            cls[k] = v;
+        }
+        int want = static_cast<int>(rest);
+        int found = 0;
+        bool done = false;
+        for (int c8 = 7; c8 >= 0 && !done; --c8) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const unsigned m = __ballot_sync(0xffffffffu, cls[k] == c8);
+                const int cnt = __popc(m);
+                if (!done) {
+                    if (want < cnt) {
+                        found = 32 * k + static_cast<int>(__fns(m, 0, want + 1));
+                        done = true;
+                    } else {
+                        want -= cnt;
+                    }
+                }
+            }
+        }
         n = found;
     }
     const int g = gp / p.passes;
