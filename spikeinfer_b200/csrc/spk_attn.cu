@@ -21,16 +21,18 @@
 
 namespace {
 
-constexpr int kWarpsPerBlock = 4;
-constexpr int kThreads = kWarpsPerBlock * 32;
+constexpr int kMaxWarps = 4;  // warps per CTA: 4, or 2 for batches of short rows (see make_plan)
 constexpr int kMaxSplits = 256;
 #ifndef SPK_ATTN_CHUNK_MAX
-#define SPK_ATTN_CHUNK_MAX 512
+#define SPK_ATTN_CHUNK_MAX 4096
 #endif
 #ifndef SPK_ATTN_MIN_BLOCKS
 #define SPK_ATTN_MIN_BLOCKS 1
 #endif
-constexpr int kTargetWarps = 148 * 4 * 4;  // four warps per scheduler
+constexpr int kWaveWarps = 148 * 12;  // warps resident at once (twelve per SM at the kernel's register count)
+#ifndef SPK_ATTN_SHORT_ROW_KEYS
+#define SPK_ATTN_SHORT_ROW_KEYS 0  // two-warp CTAs measured slower (17.7 us against 12.6 us at 64 rows x 160 keys): off
+#endif
 
 struct AttnParams {
     const uint32_t* q; int64_t sq_t, sq_n, sq_h;
@@ -42,7 +44,7 @@ struct AttnParams {
     int T; int64_t n_seqs; int Hq, Hkv, n_rep, passes;
     int bs_log2; int64_t max_blocks, num_blocks;
     float scale;
-    float* ws; int splits; int chunk_keys;
+    float* ws; int splits; int granule;  // granule: keys per CTA step, 32 x warps per CTA
     uint32_t* status;
     int64_t items;
 };
@@ -51,7 +53,8 @@ struct Plan {
     int R;        // query heads served per pass over K/V
     int passes;   // passes per KV head
     int splits;   // key ranges per sequence
-    int chunk;    // keys per range (multiple of 32)
+    int chunk;    // keys per range (multiple of the granule)
+    int warps;    // warps per CTA
     int64_t rec;  // floats per partial record
 };
 
@@ -59,23 +62,37 @@ static inline Plan make_plan(int T, int64_t n_seqs, int Hq, int Hkv, int head_di
                              int64_t max_blocks) {
     Plan p;
     const int n_rep = Hq / Hkv;
+#ifdef SPK_ATTN_SPLIT7
+    if (n_rep == 7) p.R = 4; else
+#endif
     if (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 7 || n_rep == 8) p.R = n_rep;
     else if (n_rep == 3) p.R = 4;
     else if (n_rep < 8) p.R = 8;
     else p.R = (n_rep % 7 == 0) ? 7 : 8;
     p.passes = (n_rep + p.R - 1) / p.R;
+    // One CTA serves one (row, key range); its warps take the range's 32-key tiles round-robin, so a
+    // range is a whole number of granules (one tile per warp).  Rows are cut only as far as needed to
+    // fill the GPU once, and never into ranges above SPK_ATTN_CHUNK_MAX keys, so that ragged batches
+    // balance; when every row fits one range the kernel writes the output itself and no combine
+    // launch follows.  Four warps per CTA, except for a batch of short rows that four-warp CTAs would
+    // spread over a little more than one resident wave: two-warp CTAs then keep every row resident at
+    // once (the kernel is latency bound there, and a second wave doubles its duration).
     const int64_t max_keys = max_blocks * block_size;
     const int64_t base_items = n_seqs * T * Hkv * p.passes;
-    int64_t want = base_items > 0 ? (kTargetWarps + base_items - 1) / base_items : 1;
+    p.warps = 4;
+    if (max_keys <= SPK_ATTN_SHORT_ROW_KEYS && base_items * 4 > kWaveWarps && base_items * 2 <= kWaveWarps)
+        p.warps = 2;
+    const int granule = 32 * p.warps;
+    const int64_t target = kWaveWarps / p.warps;
+    int64_t want = base_items > 0 ? (target + base_items - 1) / base_items : 1;
     if (want < 1) want = 1;
     int64_t chunk = (max_keys + want - 1) / want;
-    chunk = ((chunk + 31) / 32) * 32;
-    if (chunk < 128) chunk = 128;
+    chunk = ((chunk + granule - 1) / granule) * granule;
     if (chunk > SPK_ATTN_CHUNK_MAX) chunk = SPK_ATTN_CHUNK_MAX;
     int64_t splits = (max_keys + chunk - 1) / chunk;
     if (splits > kMaxSplits) {
         splits = kMaxSplits;
-        chunk = (((max_keys + splits - 1) / splits + 31) / 32) * 32;
+        chunk = (((max_keys + splits - 1) / splits + granule - 1) / granule) * granule;
         splits = (max_keys + chunk - 1) / chunk;
     }
     if (splits < 1) splits = 1;
@@ -108,11 +125,11 @@ struct Row {
 // Weights are kept multiplied by 2^kScaleLog2 so that the products below stay normal numbers.
 constexpr int kScaleLog2 = 40;
 
-// Keys per range of a row of `len` keys cut into at most `splits` ranges of whole tiles.
-__device__ __forceinline__ int64_t row_range_keys(int64_t len, int splits) {
-    const int64_t tiles = (len + 31) >> 5;
-    const int64_t n = tiles < splits ? (tiles > 0 ? tiles : 1) : splits;
-    return ((tiles + n - 1) / n) << 5;
+// Keys per range of a row of `len` keys cut into at most `splits` ranges of whole granules.
+__device__ __forceinline__ int64_t row_range_keys(int64_t len, int splits, int granule) {
+    const int64_t gr = (len + granule - 1) / granule;
+    const int64_t n = gr < splits ? (gr > 0 ? gr : 1) : splits;
+    return ((gr + n - 1) / n) * granule;
 }
 
 __device__ __forceinline__ void store_out(void* out, int dtype, int64_t idx, float v) {
@@ -174,7 +191,7 @@ __device__ __forceinline__ void phase_b(const uint32_t* stage, int grp, int ls, 
     const int word_off = RW::V_OFF + (ls >> 2);         // V word inside the staged row
     const bool idle = ls >= 4 * W;                      // W == 3: lanes 12..15 own no channels
     const int rot = (23 - 8 * (ls & 3)) & 31;           // rotate-left amount
-#pragma unroll
+#pragma unroll  // fully unrolled: partial unrolling (1, 2, 4) measured 6-18 % slower
     for (int it = 0; it < M::ITERS; ++it) {
         const uint32_t* row = stage + (it * M::KPI + grp) * RW::WORDS;
         float w[4 * RW::NQ];
@@ -198,23 +215,28 @@ __device__ __forceinline__ void phase_b(const uint32_t* stage, int grp, int ls, 
     }
 }
 
-template <int W, int R, bool VEC>
-__global__ void __launch_bounds__(kThreads, SPK_ATTN_MIN_BLOCKS)
+template <int W, int R, bool VEC, int NW>
+__global__ void __launch_bounds__(32 * NW, SPK_ATTN_MIN_BLOCKS)
 attn_decode_kernel(const AttnParams p) {
+    constexpr int kThreads = 32 * NW;
+    constexpr int kGranule = 32 * NW;
     using M = Map<W>;
     constexpr int D = 32 * W;
     constexpr int LUTN = D + 1;
     using RW = Row<W, R>;
-    __shared__ __align__(16) uint32_t stage_all[kWarpsPerBlock][32 * RW::WORDS];
-    // per warp: R weight tables followed by an all-zero copy that lanes past the end of the key range read
-    __shared__ float lut_all[kWarpsPerBlock][2 * R * LUTN];
+    constexpr int REC = R * D + 8;  // R*D sums, then the R weight totals (padded to 8)
+    __shared__ __align__(16) uint32_t stage_all[NW][32 * RW::WORDS];
+    // R weight tables followed by an all-zero copy that lanes past the end of the key range read
+    __shared__ float lut[2 * R * LUTN];
+    __shared__ __align__(16) float red[NW][REC];  // per-warp partial sums, folded at the end
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
-    if (item >= p.items) return;
+    // One CTA per item; its warps take the 32-key tiles of the item's key range round-robin.  Every
+    // exit below depends on the item only, so the whole CTA leaves together (barriers stay legal).
+    const int64_t item = blockIdx.x;
 
-    // item -> (n, c, gp, t): timestep fastest, so the warps of a block walk the same pages
+    // item -> (n, c, gp, t): timestep fastest, so neighbouring CTAs walk the same pages
     int64_t rest = item;
     const int t = static_cast<int>(rest % p.T); rest /= p.T;
     const int gp = static_cast<int>(rest % (p.Hkv * p.passes)); rest /= (p.Hkv * p.passes);
@@ -267,18 +289,18 @@ attn_decode_kernel(const AttnParams p) {
     int64_t len = p.lens[n];
     const int64_t max_keys = p.max_blocks << p.bs_log2;
     if (len < 1 || len > max_keys) {
-        if (lane == 0 && c == 0) spk_flag(p.status, SPK_STATUS_BAD_SEQ_LEN);
+        if (threadIdx.x == 0 && c == 0) spk_flag(p.status, SPK_STATUS_BAD_SEQ_LEN);
         len = len < 1 ? 0 : max_keys;
     }
-    // A row is cut into up to `splits` equal key ranges of whole 32-key tiles, whatever its length:
-    // short rows are spread over several warps too (short critical path when the GPU is underfilled).
-    const int64_t range = row_range_keys(len, p.splits);
+    // A row is cut into up to `splits` equal key ranges of whole granules, whatever its length: short
+    // rows are spread over several CTAs too (short critical path when the GPU is underfilled).
+    const int64_t range = row_range_keys(len, p.splits, p.granule);
     const int64_t begin = static_cast<int64_t>(c) * range;
     if (begin >= len && !(len == 0 && c == 0 && p.splits == 1)) return;
     const int64_t end = min(len, begin + range);
 
     uint32_t* stage = stage_all[warp];
-    float* lut = lut_all[warp];
+    const int64_t first = begin + 32 * warp;  // this warp's first tile; the next one is kGranule keys on
 
     // Query words of the heads served here, and their popcounts (the softmax bound).
     uint32_t qw[R][W];
@@ -325,29 +347,28 @@ attn_decode_kernel(const AttnParams p) {
         load_row<W, VEC>(vbase + static_cast<int64_t>(phys) * p.sv_blk + slot * p.sv_slot, ok, vr);
         return ok;
     };
-    int32_t phys_b = table_entry(begin + 32 + lane);  // tile 1
+    int32_t phys_b = table_entry(first + kGranule + lane);  // this warp's second tile
     uint32_t kn[W], vn[W];
-    bool ok_n = fetch(begin + lane, table_entry(begin + lane), kn, vn);
+    bool ok_n = fetch(first + lane, table_entry(first + lane), kn, vn);
 
     // (built after the first loads were issued, so their latency overlaps the exponentials)
     // Weight table: lut[hh][s] = 2^kScaleLog2 * exp((s - cmax[hh]) * scale) for s <= cmax[hh]; the
     // second half of the array stays zero.
-    for (int i = lane; i < R * LUTN; i += 32) lut[R * LUTN + i] = 0.0f;
+    for (int i = threadIdx.x; i < R * LUTN; i += kThreads) lut[R * LUTN + i] = 0.0f;
 #pragma unroll
     for (int hh = 0; hh < R; ++hh) {
-        for (int s = lane; s <= cmax[hh]; s += 32)
+        for (int s = threadIdx.x; s <= cmax[hh]; s += kThreads)
             lut[hh * LUTN + s] = ldexpf(expf(static_cast<float>(s - cmax[hh]) * p.scale), kScaleLog2);
     }
-    __syncwarp();
+    __syncthreads();
 
-
-    for (int64_t tile = begin; tile < end; tile += 32) {
+    for (int64_t tile = first; tile < end; tile += kGranule) {
         uint32_t kc[W], vc[W];
 #pragma unroll
         for (int w = 0; w < W; ++w) { kc[w] = kn[w]; vc[w] = vn[w]; }
         const bool ok_c = ok_n;
-        const int32_t phys_c = table_entry(tile + 64 + lane);
-        ok_n = fetch(tile + 32 + lane, phys_b, kn, vn);
+        const int32_t phys_c = table_entry(tile + 2 * kGranule + lane);
+        ok_n = fetch(tile + kGranule + lane, phys_b, kn, vn);
         phys_b = phys_c;
 
         // ---- phase A: lane = key ------------------------------------------------
@@ -392,30 +413,39 @@ attn_decode_kernel(const AttnParams p) {
             out_v[hh][i] *= __uint_as_float((254u - (1u << i)) << 23);
         }
     }
-    // out_v and lsum both carry the common factor 2^kScaleLog2.
+    // out_v and lsum both carry the common factor 2^kScaleLog2.  Fold the four warps through shared
+    // memory; the CTA then writes either the output row (the row has one range) or one partial record.
     const int d0 = (ls >> 2) * 32 + (ls & 3) * 8;
     const bool owner = ls < 4 * W;
+#pragma unroll
+    for (int hh = 0; hh < R; ++hh) {
+        if (owner && (hh % M::KPI) == grp) {
+            float4* o = reinterpret_cast<float4*>(&red[warp][hh * D + d0]);
+            o[0] = make_float4(out_v[hh][0], out_v[hh][1], out_v[hh][2], out_v[hh][3]);
+            o[1] = make_float4(out_v[hh][4], out_v[hh][5], out_v[hh][6], out_v[hh][7]);
+        }
+        if (lane == 0) red[warp][R * D + hh] = lsum[hh];
+    }
+    if (lane >= R && lane < 8) red[warp][R * D + lane] = 0.0f;
+    __syncthreads();
     if (p.splits == 1) {
+        for (int idx = threadIdx.x; idx < nh * D; idx += kThreads) {
+            const int hh = idx / D;
+            const int d = idx - hh * D;
+            float a = 0.0f, l = 0.0f;
 #pragma unroll
-        for (int hh = 0; hh < R; ++hh) {
-            if (hh < nh && owner && (hh % M::KPI) == grp) {
-                const int64_t o = t * p.so_t + n * p.so_n + (h0 + hh) * p.so_h + d0;
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    store_out(p.out, p.out_dtype, o + i, len > 0 ? out_v[hh][i] / lsum[hh] : 0.0f);
-            }
+            for (int w = 0; w < NW; ++w) { a += red[w][idx]; l += red[w][R * D + hh]; }
+            store_out(p.out, p.out_dtype, t * p.so_t + n * p.so_n + (h0 + hh) * p.so_h + d,
+                      len > 0 ? a / l : 0.0f);
         }
     } else {
         const int64_t rec_idx = ((n * (p.Hkv * p.passes) + gp) * p.T + t) * p.splits + c;
-        float* rec = p.ws + rec_idx * (static_cast<int64_t>(R) * D + 8);
+        float* rec = p.ws + rec_idx * REC;
+        for (int idx = threadIdx.x; idx < REC; idx += kThreads) {
+            float a = 0.0f;
 #pragma unroll
-        for (int hh = 0; hh < R; ++hh) {
-            if (owner && (hh % M::KPI) == grp) {
-                float4* o = reinterpret_cast<float4*>(rec + hh * D + d0);
-                o[0] = make_float4(out_v[hh][0], out_v[hh][1], out_v[hh][2], out_v[hh][3]);
-                o[1] = make_float4(out_v[hh][4], out_v[hh][5], out_v[hh][6], out_v[hh][7]);
-            }
-            if (lane == 0) rec[R * D + hh] = lsum[hh];
+            for (int w = 0; w < NW; ++w) a += red[w][idx];
+            rec[idx] = a;
         }
     }
 }
@@ -438,7 +468,7 @@ attn_combine_kernel(const AttnParams p, int D) {
     const int64_t max_keys = p.max_blocks << p.bs_log2;
     if (len < 1) len = 0;
     if (len > max_keys) len = max_keys;
-    const int64_t range = row_range_keys(len, p.splits);
+    const int64_t range = row_range_keys(len, p.splits, p.granule);
     const int n_splits = static_cast<int>((len + range - 1) / range);
     const int64_t rec_floats = static_cast<int64_t>(R) * D + 8;
     const float* base = p.ws + grp_item * p.splits * rec_floats;
@@ -455,14 +485,14 @@ attn_combine_kernel(const AttnParams p, int D) {
     }
 }
 
-template <int W, int R>
-int launch_attn(const AttnParams& p, bool vec, cudaStream_t stream) {
-    const int64_t blocks = (p.items + kWarpsPerBlock - 1) / kWarpsPerBlock;
+template <int W, int R, int NW>
+int launch_attn_nw(const AttnParams& p, bool vec, cudaStream_t stream) {
+    const int64_t blocks = p.items;
     if (blocks > 0x7fffffffLL) return SPK_ERR_TOO_LARGE;
     if (vec && (W == 2 || W == 4))
-        attn_decode_kernel<W, R, true><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(p);
+        attn_decode_kernel<W, R, true, NW><<<static_cast<unsigned>(blocks), 32 * NW, 0, stream>>>(p);
     else
-        attn_decode_kernel<W, R, false><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(p);
+        attn_decode_kernel<W, R, false, NW><<<static_cast<unsigned>(blocks), 32 * NW, 0, stream>>>(p);
     SPK_CHECK_LAUNCH();
     if (p.splits > 1) {
         const int64_t groups = p.items / p.splits;
@@ -470,6 +500,11 @@ int launch_attn(const AttnParams& p, bool vec, cudaStream_t stream) {
         SPK_CHECK_LAUNCH();
     }
     return SPK_OK;
+}
+
+template <int W, int R>
+int launch_attn(const AttnParams& p, bool vec, cudaStream_t stream) {
+    return p.granule == 64 ? launch_attn_nw<W, R, 2>(p, vec, stream) : launch_attn_nw<W, R, 4>(p, vec, stream);
 }
 
 template <int W>
@@ -608,7 +643,7 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
     p.T = T; p.n_seqs = n_seqs; p.Hq = num_q_heads; p.Hkv = num_kv_heads;
     p.n_rep = num_q_heads / num_kv_heads; p.passes = pl.passes;
     p.bs_log2 = bs_log2; p.max_blocks = max_blocks; p.num_blocks = num_blocks;
-    p.scale = scale; p.ws = static_cast<float*>(workspace); p.splits = pl.splits; p.chunk_keys = pl.chunk;
+    p.scale = scale; p.ws = static_cast<float*>(workspace); p.splits = pl.splits; p.granule = 32 * pl.warps;
     p.status = status;
     p.items = n_seqs * T * num_kv_heads * pl.passes * pl.splits;
 
