@@ -4,35 +4,52 @@
 // (spikeinfer/kernels/spike_attention.py:67-150 of the reference).
 //
 // Formulation used here:
-//  * A warp owns one work item = (sequence, timestep, KV head, key range) and serves all query
-//    heads of the GQA group from a single read of K and V.
+//  * A CTA owns one work item = (sequence, timestep, KV head, key range) and serves all query heads
+//    of the GQA group (eight per pass) from a single read of K and V; its warps take the range's
+//    32-key tiles round-robin and fold their partial sums through shared memory at the end.
 //  * popc(q & k) <= popc(q), so the softmax is taken against the fixed bound m = popc(q)*scale
-//    instead of a running maximum.  That is the same softmax (a common factor cancels), it cannot
-//    overflow, and the smallest weight, exp(-head_dim*scale), is far above fp32 underflow.  Partial
-//    sums of different key ranges therefore combine by plain addition.
+//    instead of a running maximum.  That is the same softmax (a common factor cancels) and it cannot
+//    overflow.  Partial sums of different key ranges therefore combine by plain addition.
 //  * A score is an integer in [0, popc(q)], so a weight takes at most head_dim+1 values: they come
 //    from a per-item table in shared memory, indexed by the exact integer score.
-//  * Phase A (lane = key): coalesced K/V row loads, scores with __popc, weights from the table,
-//    staged to shared memory together with the V words.
-//    Phase B (lane = channel group): every staged key is broadcast; a lane adds the key's weight to
-//    the accumulators of the channels whose V bit is set ("bit-selected sum"), fp32.
-//  * No tensor cores: the operands are 1-bit and the contraction is a conditional add.
+//  * The weighted sum over keys is a small matrix product, heads x keys times keys x channels, with a
+//    0/1 right-hand side.  It runs on the tensor cores as m16n8k16 fp16 MMAs with fp32 accumulation:
+//      - left operand: the weight of (head, key), split into two fp16 numbers hi + lo * 2^-11 that
+//        occupy rows h and h + 8 of the 16-row tile (22 significant bits together; the table holds
+//        the pair ready-made);
+//      - right operand: the V bit of (key, channel) used IN PLACE as an fp16 number.  A byte of the V
+//        row is moved into the low byte of a half-word and all bits but one are masked off; what is
+//        left is either 0 or the fp16 subnormal 2^(i-24) for bit i.  Products with it are exact, and
+//        the known power of two is removed from the accumulators once, after the last key;
+//      - an extra all-ones column block yields the softmax denominators from the same MMAs.
+//    One 32-key tile of a 64-channel head costs 18 MMAs and about 200 instructions per warp, against
+//    about 620 instructions for the same tile as fp32 bit-selected adds on the SIMT pipes.
 #include "spk_common.cuh"
 
 namespace {
 
-constexpr int kMaxWarps = 4;  // warps per CTA: 4, or 2 for batches of short rows (see make_plan)
+#ifndef SPK_ATTN_WARPS
+#define SPK_ATTN_WARPS 4
+#endif
+constexpr int kWarps = SPK_ATTN_WARPS;  // warps per CTA
+constexpr int kThreads = 32 * kWarps;
+constexpr int kGranule = 32 * kWarps;  // keys per CTA step: one 32-key tile per warp
+constexpr int kHeads = 8;             // query heads per pass: rows 0..7 (hi) and 8..15 (lo) of the MMA tile
 constexpr int kMaxSplits = 256;
 #ifndef SPK_ATTN_CHUNK_MAX
 #define SPK_ATTN_CHUNK_MAX 4096
 #endif
 #ifndef SPK_ATTN_MIN_BLOCKS
-#define SPK_ATTN_MIN_BLOCKS 1
+#define SPK_ATTN_MIN_BLOCKS (16 / SPK_ATTN_WARPS)  // 128 registers: sixteen warps per SM
 #endif
-constexpr int kWaveWarps = 148 * 12;  // warps resident at once (twelve per SM at the kernel's register count)
-#ifndef SPK_ATTN_SHORT_ROW_KEYS
-#define SPK_ATTN_SHORT_ROW_KEYS 0  // two-warp CTAs measured slower (17.7 us against 12.6 us at 64 rows x 160 keys): off
+#ifndef SPK_ATTN_TARGET_CTAS
+#define SPK_ATTN_TARGET_CTAS (148 * 3)
 #endif
+// Weights are kept multiplied by 2^kScaleLog2: the largest (score = bound) is 2^14, inside the fp16
+// range, and the fp16 pair stays accurate down to exp(-24) of it.
+constexpr int kScaleLog2 = 14;
+constexpr float kMaxExponentRange = 24.0f;  // head_dim * scale above this is refused
+constexpr float kLoUnscale = 1.0f / 2048.0f;  // the lo half of a weight is stored times 2^11
 
 struct AttnParams {
     const uint32_t* q; int64_t sq_t, sq_n, sq_h;
@@ -44,17 +61,15 @@ struct AttnParams {
     int T; int64_t n_seqs; int Hq, Hkv, n_rep, passes;
     int bs_log2; int64_t max_blocks, num_blocks;
     float scale;
-    float* ws; int splits; int granule;  // granule: keys per CTA step, 32 x warps per CTA
+    float* ws; int splits;
     uint32_t* status;
     int64_t items;
 };
 
 struct Plan {
-    int R;        // query heads served per pass over K/V
-    int passes;   // passes per KV head
+    int passes;   // passes per KV head (eight query heads each)
     int splits;   // key ranges per sequence
     int chunk;    // keys per range (multiple of the granule)
-    int warps;    // warps per CTA
     int64_t rec;  // floats per partial record
 };
 
@@ -62,74 +77,35 @@ static inline Plan make_plan(int T, int64_t n_seqs, int Hq, int Hkv, int head_di
                              int64_t max_blocks) {
     Plan p;
     const int n_rep = Hq / Hkv;
-#ifdef SPK_ATTN_SPLIT7
-    if (n_rep == 7) p.R = 4; else
-#endif
-    if (n_rep == 1 || n_rep == 2 || n_rep == 4 || n_rep == 7 || n_rep == 8) p.R = n_rep;
-    else if (n_rep == 3) p.R = 4;
-    else if (n_rep < 8) p.R = 8;
-    else p.R = (n_rep % 7 == 0) ? 7 : 8;
-    p.passes = (n_rep + p.R - 1) / p.R;
-    // One CTA serves one (row, key range); its warps take the range's 32-key tiles round-robin, so a
-    // range is a whole number of granules (one tile per warp).  Rows are cut only as far as needed to
-    // fill the GPU once, and never into ranges above SPK_ATTN_CHUNK_MAX keys, so that ragged batches
-    // balance; when every row fits one range the kernel writes the output itself and no combine
-    // launch follows.  Four warps per CTA, except for a batch of short rows that four-warp CTAs would
-    // spread over a little more than one resident wave: two-warp CTAs then keep every row resident at
-    // once (the kernel is latency bound there, and a second wave doubles its duration).
+    p.passes = (n_rep + kHeads - 1) / kHeads;
+    // A range is a whole number of granules.  Rows are cut only as far as needed to fill the GPU once,
+    // and never into ranges above SPK_ATTN_CHUNK_MAX keys; when every row fits one range the kernel
+    // writes the output itself and no combine launch follows.
     const int64_t max_keys = max_blocks * block_size;
     const int64_t base_items = n_seqs * T * Hkv * p.passes;
-    p.warps = 4;
-    if (max_keys <= SPK_ATTN_SHORT_ROW_KEYS && base_items * 4 > kWaveWarps && base_items * 2 <= kWaveWarps)
-        p.warps = 2;
-    const int granule = 32 * p.warps;
-    const int64_t target = kWaveWarps / p.warps;
-    int64_t want = base_items > 0 ? (target + base_items - 1) / base_items : 1;
+    int64_t want = base_items > 0 ? (SPK_ATTN_TARGET_CTAS + base_items - 1) / base_items : 1;
     if (want < 1) want = 1;
     int64_t chunk = (max_keys + want - 1) / want;
-    chunk = ((chunk + granule - 1) / granule) * granule;
+    chunk = ((chunk + kGranule - 1) / kGranule) * kGranule;
     if (chunk > SPK_ATTN_CHUNK_MAX) chunk = SPK_ATTN_CHUNK_MAX;
     int64_t splits = (max_keys + chunk - 1) / chunk;
     if (splits > kMaxSplits) {
         splits = kMaxSplits;
-        chunk = (((max_keys + splits - 1) / splits + granule - 1) / granule) * granule;
+        chunk = (((max_keys + splits - 1) / splits + kGranule - 1) / kGranule) * kGranule;
         splits = (max_keys + chunk - 1) / chunk;
     }
     if (splits < 1) splits = 1;
     p.splits = static_cast<int>(splits);
     p.chunk = static_cast<int>(chunk);
-    p.rec = static_cast<int64_t>(p.R) * head_dim + 8;  // R*D sums, then R (padded to 8) weight totals
+    p.rec = static_cast<int64_t>(kHeads) * head_dim + 8;  // 8*D sums, then the 8 weight totals
     return p;
 }
 
-template <int W>
-struct Map {
-    // Phase-B lane mapping: a key is served by LPK lanes, lane `ls` of the group owns the 8 channels
-    // of byte `ls` of the V row (word ls / 4, byte ls % 4).  KPI keys are processed per iteration.
-    static constexpr int LPK = (W == 1) ? 4 : (W == 2) ? 8 : 16;
-    static constexpr int KPI = 32 / LPK;
-    static constexpr int ITERS = 32 / KPI;
-};
-
-// Staged row of one key: the R weights (padded to a multiple of 4 words), then the V words.  The row
-// length is an odd multiple of 4 words so that both the per-key 16-byte stores of phase A and the
-// per-group 16-byte broadcast loads of phase B are free of bank conflicts.
-template <int W, int R>
-struct Row {
-    static constexpr int NQ = (R + 3) / 4;  // 16-byte loads that cover the weights
-    static constexpr int V_OFF = (R + W <= 4 * NQ) ? R : 4 * NQ;
-    static constexpr int NEED = ((V_OFF + W + 3) / 4) * 4;
-    static constexpr int WORDS = (NEED / 4) % 2 == 1 ? NEED : NEED + 4;
-};
-
-// Weights are kept multiplied by 2^kScaleLog2 so that the products below stay normal numbers.
-constexpr int kScaleLog2 = 40;
-
 // Keys per range of a row of `len` keys cut into at most `splits` ranges of whole granules.
-__device__ __forceinline__ int64_t row_range_keys(int64_t len, int splits, int granule) {
-    const int64_t gr = (len + granule - 1) / granule;
+__device__ __forceinline__ int64_t row_range_keys(int64_t len, int splits) {
+    const int64_t gr = (len + kGranule - 1) / kGranule;
     const int64_t n = gr < splits ? (gr > 0 ? gr : 1) : splits;
-    return ((gr + n - 1) / n) * granule;
+    return ((gr + n - 1) / n) * kGranule;
 }
 
 __device__ __forceinline__ void store_out(void* out, int dtype, int64_t idx, float v) {
@@ -138,18 +114,20 @@ __device__ __forceinline__ void store_out(void* out, int dtype, int64_t idx, flo
     else static_cast<__half*>(out)[idx] = __float2half_rn(v);
 }
 
-// Packed pair of fp32 values in one 64-bit register (the operand type of the f32x2 instructions).
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
 }
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-// acc = a * b + acc on both halves (one instruction, two fp32 FMAs).
-__device__ __forceinline__ void fma2(uint64_t& acc, uint64_t a, uint64_t b) {
-    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+
+// c += a (16x16 fp16, row major) * b (16x8 fp16, column major), fp32 accumulators.  Thread (gid =
+// lane / 4, tig = lane % 4) holds a0 = A[gid][2tig..], a1 = A[gid+8][2tig..], a2 = A[gid][2tig+8..],
+// a3 = A[gid+8][2tig+8..]; b0 = B[2tig..][gid], b1 = B[2tig+8..][gid]; c0,c1 = C[gid][2tig, 2tig+1],
+// c2,c3 = C[gid+8][2tig, 2tig+1] (two consecutive elements per register, lower index in the low half).
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
 // Loads the W words of one K or V row.  VEC: the row is W-word aligned and may be read with one
@@ -171,69 +149,101 @@ __device__ __forceinline__ void load_row(const uint32_t* p, bool ok, uint32_t (&
     }
 }
 
-// Phase B of one 32-key tile: every staged key is broadcast to the LPK lanes that serve it; a lane adds
-// the key's weights to the accumulators of those of its 8 channels whose V bit is set.
-//
-// The V byte a lane owns is rotated so that its 8 bits sit at bit positions 23..30 of a register;
-// masking one of those bits and reading the result as fp32 gives either 0 or the power of two
-// c_i = 2^(2^i - 127).  fma(weight, that, acc) therefore IS the bit-selected add, scaled by c_i; the
-// scale is exact (no product leaves the normal range, see kScaleLog2) and is removed once, after the
-// last key.  Two channels share one f32x2 FMA.  Measured on B200, this form beats per-bit predicated
-// adds (47 us against 68-73 us per call at 64 sequences x [128, 4096] keys) and scalar FMAs on the
-// same masks (51 us against 60 us).
-typedef uint64_t AccT;    // two channels per f32x2 accumulator
-constexpr int kAccPerLane = 4;
-
-template <int W, int R>
-__device__ __forceinline__ void phase_b(const uint32_t* stage, int grp, int ls, AccT (&acc)[R][kAccPerLane]) {
-    using M = Map<W>;
-    using RW = Row<W, R>;
-    const int word_off = RW::V_OFF + (ls >> 2);         // V word inside the staged row
-    const bool idle = ls >= 4 * W;                      // W == 3: lanes 12..15 own no channels
-    const int rot = (23 - 8 * (ls & 3)) & 31;           // rotate-left amount
-#pragma unroll  // fully unrolled: partial unrolling (1, 2, 4) measured 6-18 % slower
-    for (int it = 0; it < M::ITERS; ++it) {
-        const uint32_t* row = stage + (it * M::KPI + grp) * RW::WORDS;
-        float w[4 * RW::NQ];
+// Stores one staged row (W words, W-word aligned) with a single access where the width allows.
+template <int W>
+__device__ __forceinline__ void store_row(uint32_t* p, const uint32_t (&r)[W]) {
+    if (W == 2) *reinterpret_cast<uint2*>(p) = make_uint2(r[0], r[1]);
+    else if (W == 4) *reinterpret_cast<uint4*>(p) = make_uint4(r[0], r[1], r[2], r[3]);
+    else {
 #pragma unroll
-        for (int j = 0; j < RW::NQ; ++j) {
-            const float4 t = *reinterpret_cast<const float4*>(row + 4 * j);
-            w[4 * j] = t.x; w[4 * j + 1] = t.y; w[4 * j + 2] = t.z; w[4 * j + 3] = t.w;
-        }
-        uint32_t v = idle ? 0u : row[word_off];
-        v = __funnelshift_l(v, v, rot);
-        uint64_t m[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-            m[i] = pack2(__uint_as_float(v & (1u << (23 + 2 * i))), __uint_as_float(v & (1u << (24 + 2 * i))));
-#pragma unroll
-        for (int hh = 0; hh < R; ++hh) {
-            const uint64_t w2 = pack2(w[hh], w[hh]);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) fma2(acc[hh][i], w2, m[i]);
-        }
+        for (int w = 0; w < W; ++w) p[w] = r[w];
     }
 }
 
-template <int W, int R, bool VEC, int NW>
-__global__ void __launch_bounds__(32 * NW, SPK_ATTN_MIN_BLOCKS)
+// Two adjacent staged rows (keys k and k + 1, k even): 2W consecutive words, 8W-byte aligned.
+template <int W>
+__device__ __forceinline__ void load_pair(const uint32_t* p, uint32_t (&r0)[W], uint32_t (&r1)[W]) {
+    if (W == 1) {
+        const uint2 t = *reinterpret_cast<const uint2*>(p);
+        r0[0] = t.x; r1[0] = t.y;
+    } else if (W == 2) {
+        const uint4 t = *reinterpret_cast<const uint4*>(p);
+        r0[0] = t.x; r0[1] = t.y; r1[0] = t.z; r1[1] = t.w;
+    } else {
+#pragma unroll
+        for (int w = 0; w < W; ++w) { r0[w] = p[w]; r1[w] = p[W + w]; }
+    }
+}
+
+// One 32-key tile of a warp, from the staged K and V rows.  ALL: every key of the tile is live
+// (`live` is all ones); otherwise keys whose bit in `live` is clear get weight zero.
+//
+// The MMAs accumulate in place over all tiles of the warp.  Against an fp64 evaluation the result is off
+// by 6.0e-7 (relative to the largest output) after 32768 keys; starting every MMA from zero and adding
+// its result with an ordinary fp32 add gave the same figure, so the in-place form loses nothing.
+template <int W, bool ALL>
+__device__ __forceinline__ void tile_mma(const uint32_t* kst, const uint32_t* vst, const uint32_t (&qw)[W],
+                                         const uint32_t* my_lut, const uint32_t* zero_lut, unsigned live,
+                                         int gid, int tig, float (&acc)[4 * W][4], float (&accl)[4]) {
+    const uint32_t gmask = (1u << gid) | (1u << (16 + gid));  // bit gid of both half-words
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+        // this thread's keys of the 16-key step: k0, k0 + 1, k0 + 8, k0 + 9
+        const int k0 = 16 * ks + 2 * tig;
+        uint32_t kw[4][W], vw[4][W];
+        load_pair<W>(kst + k0 * W, kw[0], kw[1]);
+        load_pair<W>(kst + (k0 + 8) * W, kw[2], kw[3]);
+        load_pair<W>(vst + k0 * W, vw[0], vw[1]);
+        load_pair<W>(vst + (k0 + 8) * W, vw[2], vw[3]);
+        // weights of (head gid, these keys): {hi, lo} fp16 pairs from the table, indexed by bound - score
+        uint32_t wt[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            int s = 0;
+#pragma unroll
+            for (int w = 0; w < W; ++w) s += __popc(qw[w] & kw[i][w]);
+            const int key = k0 + (i & 1) + 8 * (i >> 1);
+            const uint32_t* tab = (ALL || ((live >> key) & 1u)) ? my_lut : zero_lut;
+            wt[i] = tab[-s];
+        }
+        uint32_t a[4];
+        a[0] = prmt(wt[0], wt[1], 0x5410);  // hi(k0), hi(k0+1)      -> row gid
+        a[1] = prmt(wt[0], wt[1], 0x7632);  // lo(k0), lo(k0+1)      -> row gid + 8
+        a[2] = prmt(wt[2], wt[3], 0x5410);  // hi(k0+8), hi(k0+9)
+        a[3] = prmt(wt[2], wt[3], 0x7632);
+        // V bits of channel 8j + gid for the same keys, as fp16: byte (j % 4) of word j / 4 goes to the
+        // low byte of each half-word, then everything but bit gid is masked off.
+#pragma unroll
+        for (int j = 0; j < 4 * W; ++j) {
+            const int w = j >> 2;
+            const uint32_t b = j & 3;
+            const uint32_t sel = b | (b << 4) | ((4u + b) << 8) | ((4u + b) << 12);
+            mma16816(acc[j], a, prmt(vw[0][w], vw[1][w], sel) & gmask, prmt(vw[2][w], vw[3][w], sel) & gmask);
+        }
+        mma16816(accl, a, 0x3C003C00u, 0x3C003C00u);  // ones: the weight totals
+    }
+}
+
+template <int W, bool VEC>
+__global__ void __launch_bounds__(kThreads, SPK_ATTN_MIN_BLOCKS)
 attn_decode_kernel(const AttnParams p) {
-    constexpr int kThreads = 32 * NW;
-    constexpr int kGranule = 32 * NW;
-    using M = Map<W>;
     constexpr int D = 32 * W;
     constexpr int LUTN = D + 1;
-    using RW = Row<W, R>;
-    constexpr int REC = R * D + 8;  // R*D sums, then the R weight totals (padded to 8)
-    __shared__ __align__(16) uint32_t stage_all[NW][32 * RW::WORDS];
-    // R weight tables followed by an all-zero copy that lanes past the end of the key range read
-    __shared__ float lut[2 * R * LUTN];
-    __shared__ __align__(16) float red[NW][REC];  // per-warp partial sums, folded at the end
+    constexpr int REC = kHeads * D + 8;  // 8*D sums, then the 8 weight totals
+    __shared__ __align__(16) uint32_t kst_all[kWarps][32 * W];
+    __shared__ __align__(16) uint32_t vst_all[kWarps][32 * W];
+    // weight table ({hi, lo} fp16 pairs, indexed by bound - score) and an all-zero one for dead keys
+    // and absent heads
+    __shared__ uint32_t lut[2 * LUTN];
+    // per-warp partial sums, folded at the end; head rows padded by 8 floats against bank conflicts
+    constexpr int RS = D + 8;
+    __shared__ __align__(16) float red[kWarps][kHeads * RS + 8];
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    // One CTA per item; its warps take the 32-key tiles of the item's key range round-robin.  Every
-    // exit below depends on the item only, so the whole CTA leaves together (barriers stay legal).
+    const int gid = lane >> 2;  // MMA row group: the query head this thread weighs keys for
+    const int tig = lane & 3;
+    // One CTA per item; every exit below depends on the item only, so the whole CTA leaves together.
     const int64_t item = blockIdx.x;
 
     // item -> (n, c, gp, t): timestep fastest, so neighbouring CTAs walk the same pages
@@ -283,8 +293,8 @@ attn_decode_kernel(const AttnParams p) {
     }
     const int g = gp / p.passes;
     const int pass = gp - g * p.passes;
-    const int h0 = g * p.n_rep + pass * R;
-    const int nh = min(R, p.n_rep - pass * R);
+    const int h0 = g * p.n_rep + pass * kHeads;
+    const int nh = min(kHeads, p.n_rep - pass * kHeads);
 
     int64_t len = p.lens[n];
     const int64_t max_keys = p.max_blocks << p.bs_log2;
@@ -294,45 +304,35 @@ attn_decode_kernel(const AttnParams p) {
     }
     // A row is cut into up to `splits` equal key ranges of whole granules, whatever its length: short
     // rows are spread over several CTAs too (short critical path when the GPU is underfilled).
-    const int64_t range = row_range_keys(len, p.splits, p.granule);
+    const int64_t range = row_range_keys(len, p.splits);
     const int64_t begin = static_cast<int64_t>(c) * range;
     if (begin >= len && !(len == 0 && c == 0 && p.splits == 1)) return;
     const int64_t end = min(len, begin + range);
 
-    uint32_t* stage = stage_all[warp];
+    uint32_t* kst = kst_all[warp];
+    uint32_t* vst = vst_all[warp];
     const int64_t first = begin + 32 * warp;  // this warp's first tile; the next one is kGranule keys on
 
-    // Query words of the heads served here, and their popcounts (the softmax bound).
-    uint32_t qw[R][W];
-    int cmax[R];
+    // Query words of this thread's head and their popcount (the softmax bound).
+    uint32_t qw[W];
+    int cmax = 0;
 #pragma unroll
-    for (int hh = 0; hh < R; ++hh) {
-        cmax[hh] = 0;
-#pragma unroll
-        for (int w = 0; w < W; ++w) {
-            qw[hh][w] = 0;
-            if (hh < nh) qw[hh][w] = __ldg(p.q + t * p.sq_t + n * p.sq_n + (h0 + hh) * p.sq_h + w);
-            cmax[hh] += __popc(qw[hh][w]);
-        }
+    for (int w = 0; w < W; ++w) {
+        qw[w] = gid < nh ? __ldg(p.q + t * p.sq_t + n * p.sq_n + (h0 + gid) * p.sq_h + w) : 0u;
+        cmax += __popc(qw[w]);
     }
-    AccT acc[R][kAccPerLane];
-    float lsum[R];
+    float acc[4 * W][4], accl[4];
 #pragma unroll
-    for (int hh = 0; hh < R; ++hh) {
-        lsum[hh] = 0.0f;
-#pragma unroll
-        for (int i = 0; i < kAccPerLane; ++i) acc[hh][i] = 0;
-    }
+    for (int j = 0; j < 4 * W; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+    accl[0] = accl[1] = accl[2] = accl[3] = 0.0f;
 
     const uint32_t* kbase = p.k + t * p.sk_t + g * p.sk_h;
     const uint32_t* vbase = p.v + t * p.sv_t + g * p.sv_h;
     const int32_t* table = p.tables + n * p.sbt_n;
     const int bs_mask = (1 << p.bs_log2) - 1;
-    const int grp = lane / M::LPK;
-    const int ls = lane - grp * M::LPK;
 
-    // Three-stage software pipeline over 32-key tiles: block-table entry of tile i+2, K/V rows of
-    // tile i+1, arithmetic of tile i.
+    // Three-stage software pipeline over this warp's tiles: block-table entry of the tile after next,
+    // K/V rows of the next tile (lane = key, coalesced), arithmetic of the current one.
     auto table_entry = [&](int64_t key) -> int32_t {
         return key < end ? __ldg(table + (key >> p.bs_log2)) : -1;
     };
@@ -352,81 +352,51 @@ attn_decode_kernel(const AttnParams p) {
     bool ok_n = fetch(first + lane, table_entry(first + lane), kn, vn);
 
     // (built after the first loads were issued, so their latency overlaps the exponentials)
-    // Weight table: lut[hh][s] = 2^kScaleLog2 * exp((s - cmax[hh]) * scale) for s <= cmax[hh]; the
-    // second half of the array stays zero.
-    for (int i = threadIdx.x; i < R * LUTN; i += kThreads) lut[R * LUTN + i] = 0.0f;
-#pragma unroll
-    for (int hh = 0; hh < R; ++hh) {
-        for (int s = threadIdx.x; s <= cmax[hh]; s += kThreads)
-            lut[hh * LUTN + s] = ldexpf(expf(static_cast<float>(s - cmax[hh]) * p.scale), kScaleLog2);
+    // A weight depends on bound - score only: lut[d] = {hi, lo} with hi + lo * 2^-11 =
+    // 2^kScaleLog2 * exp(-d * scale), d = 0..head_dim, shared by all heads.
+    for (int i = threadIdx.x; i < 2 * LUTN; i += kThreads) {
+        uint32_t e = 0u;
+        if (i < LUTN) {
+            const float wv = ldexpf(expf(-static_cast<float>(i) * p.scale), kScaleLog2);
+            const __half hi = __float2half_rn(wv);
+            const __half lo = __float2half_rn((wv - __half2float(hi)) * 2048.0f);
+            e = static_cast<uint32_t>(__half_as_ushort(hi)) | (static_cast<uint32_t>(__half_as_ushort(lo)) << 16);
+        }
+        lut[i] = e;
     }
     __syncthreads();
+    // tables are indexed with -score from these bases: live keys of a present head read lut[cmax - s],
+    // everything else reads a zero (cmax <= head_dim keeps both inside their table)
+    const uint32_t* zero_lut = lut + LUTN + cmax;
+    const uint32_t* my_lut = gid < nh ? lut + cmax : zero_lut;
 
     for (int64_t tile = first; tile < end; tile += kGranule) {
-        uint32_t kc[W], vc[W];
-#pragma unroll
-        for (int w = 0; w < W; ++w) { kc[w] = kn[w]; vc[w] = vn[w]; }
-        const bool ok_c = ok_n;
+        // ---- stage the current tile (lane = key) and start the next one's loads --------------------
+        store_row<W>(kst + lane * W, kn);
+        store_row<W>(vst + lane * W, vn);
+        const unsigned live = __ballot_sync(0xffffffffu, ok_n);
         const int32_t phys_c = table_entry(tile + 2 * kGranule + lane);
         ok_n = fetch(tile + kGranule + lane, phys_b, kn, vn);
         phys_b = phys_c;
-
-        // ---- phase A: lane = key ------------------------------------------------
-        const float* my_lut = lut + (ok_c ? 0 : R * LUTN);
-        uint32_t rowv[RW::WORDS];
-#pragma unroll
-        for (int i = 0; i < RW::WORDS; ++i) rowv[i] = 0u;
-#pragma unroll
-        for (int hh = 0; hh < R; ++hh) {
-            int s = 0;
-#pragma unroll
-            for (int w = 0; w < W; ++w) s += __popc(qw[hh][w] & kc[w]);
-            const float wv = my_lut[hh * LUTN + s];
-            rowv[hh] = __float_as_uint(wv);
-            lsum[hh] += wv;
-        }
-#pragma unroll
-        for (int w = 0; w < W; ++w) rowv[RW::V_OFF + w] = vc[w];
-        uint4* row = reinterpret_cast<uint4*>(stage + lane * RW::WORDS);
-#pragma unroll
-        for (int j = 0; j < RW::NEED / 4; ++j)
-            row[j] = make_uint4(rowv[4 * j], rowv[4 * j + 1], rowv[4 * j + 2], rowv[4 * j + 3]);
         __syncwarp();
-        // ---- phase B: lane = (key group, V byte) ---------------------------------
-        phase_b<W, R>(stage, grp, ls, acc);
+        // ---- weights and weighted sums on the tensor cores (lane = (head, key quad)) -----------------
+        if (live == 0xffffffffu) tile_mma<W, true>(kst, vst, qw, my_lut, zero_lut, live, gid, tig, acc, accl);
+        else tile_mma<W, false>(kst, vst, qw, my_lut, zero_lut, live, gid, tig, acc, accl);
         __syncwarp();
     }
 
-    // ---- reduce: weights over all lanes, accumulators over the key groups; undo the scales ---
-    float out_v[R][8];
+    // ---- undo the scales; fold the warps; write the output row or one partial record --------------
+    // Column n of a channel block was multiplied by 2^(n - 24) (the V bit read as fp16); the lo rows by
+    // 2^11.  Sums and totals both keep the common factor 2^kScaleLog2.
+    const float u0 = __uint_as_float(static_cast<uint32_t>(127 + 24 - 2 * tig) << 23);
+    const float u1 = __uint_as_float(static_cast<uint32_t>(127 + 23 - 2 * tig) << 23);
 #pragma unroll
-    for (int hh = 0; hh < R; ++hh) {
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) lsum[hh] += __shfl_xor_sync(0xffffffffu, lsum[hh], o);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) unpack2(acc[hh][i], out_v[hh][2 * i], out_v[hh][2 * i + 1]);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-#pragma unroll
-            for (int o = 16; o >= M::LPK; o >>= 1) out_v[hh][i] += __shfl_xor_sync(0xffffffffu, out_v[hh][i], o);
-            // channel i carries the factor 2^(2^i - 127)
-            out_v[hh][i] *= __uint_as_float((254u - (1u << i)) << 23);
-        }
+    for (int j = 0; j < 4 * W; ++j) {
+        const float v0 = (acc[j][0] + acc[j][2] * kLoUnscale) * u0;
+        const float v1 = (acc[j][1] + acc[j][3] * kLoUnscale) * u1;
+        *reinterpret_cast<float2*>(&red[warp][gid * RS + 8 * j + 2 * tig]) = make_float2(v0, v1);
     }
-    // out_v and lsum both carry the common factor 2^kScaleLog2.  Fold the four warps through shared
-    // memory; the CTA then writes either the output row (the row has one range) or one partial record.
-    const int d0 = (ls >> 2) * 32 + (ls & 3) * 8;
-    const bool owner = ls < 4 * W;
-#pragma unroll
-    for (int hh = 0; hh < R; ++hh) {
-        if (owner && (hh % M::KPI) == grp) {
-            float4* o = reinterpret_cast<float4*>(&red[warp][hh * D + d0]);
-            o[0] = make_float4(out_v[hh][0], out_v[hh][1], out_v[hh][2], out_v[hh][3]);
-            o[1] = make_float4(out_v[hh][4], out_v[hh][5], out_v[hh][6], out_v[hh][7]);
-        }
-        if (lane == 0) red[warp][R * D + hh] = lsum[hh];
-    }
-    if (lane >= R && lane < 8) red[warp][R * D + lane] = 0.0f;
+    if (tig == 0) red[warp][kHeads * RS + gid] = accl[0] + accl[2] * kLoUnscale;
     __syncthreads();
     if (p.splits == 1) {
         for (int idx = threadIdx.x; idx < nh * D; idx += kThreads) {
@@ -434,7 +404,7 @@ attn_decode_kernel(const AttnParams p) {
             const int d = idx - hh * D;
             float a = 0.0f, l = 0.0f;
 #pragma unroll
-            for (int w = 0; w < NW; ++w) { a += red[w][idx]; l += red[w][R * D + hh]; }
+            for (int w = 0; w < kWarps; ++w) { a += red[w][hh * RS + d]; l += red[w][kHeads * RS + hh]; }
             store_out(p.out, p.out_dtype, t * p.so_t + n * p.so_n + (h0 + hh) * p.so_h + d,
                       len > 0 ? a / l : 0.0f);
         }
@@ -442,16 +412,17 @@ attn_decode_kernel(const AttnParams p) {
         const int64_t rec_idx = ((n * (p.Hkv * p.passes) + gp) * p.T + t) * p.splits + c;
         float* rec = p.ws + rec_idx * REC;
         for (int idx = threadIdx.x; idx < REC; idx += kThreads) {
+            const int hh = idx / D;  // 8: the weight totals
+            const int src = hh * RS + (idx - hh * D);
             float a = 0.0f;
 #pragma unroll
-            for (int w = 0; w < NW; ++w) a += red[w][idx];
+            for (int w = 0; w < kWarps; ++w) a += red[w][src];
             rec[idx] = a;
         }
     }
 }
 
 // Sums the partial records of a (sequence, timestep, KV head, pass) in key-range order and divides.
-template <int R>
 __global__ void __launch_bounds__(128)
 attn_combine_kernel(const AttnParams p, int D) {
     const int64_t grp_item = blockIdx.x;  // (n, gp, t)
@@ -461,16 +432,16 @@ attn_combine_kernel(const AttnParams p, int D) {
     const int64_t n = rest;
     const int g = gp / p.passes;
     const int pass = gp - g * p.passes;
-    const int h0 = g * p.n_rep + pass * R;
-    const int nh = min(R, p.n_rep - pass * R);
+    const int h0 = g * p.n_rep + pass * kHeads;
+    const int nh = min(kHeads, p.n_rep - pass * kHeads);
 
     int64_t len = p.lens[n];
     const int64_t max_keys = p.max_blocks << p.bs_log2;
     if (len < 1) len = 0;
     if (len > max_keys) len = max_keys;
-    const int64_t range = row_range_keys(len, p.splits, p.granule);
+    const int64_t range = row_range_keys(len, p.splits);
     const int n_splits = static_cast<int>((len + range - 1) / range);
-    const int64_t rec_floats = static_cast<int64_t>(R) * D + 8;
+    const int64_t rec_floats = static_cast<int64_t>(kHeads) * D + 8;
     const float* base = p.ws + grp_item * p.splits * rec_floats;
     for (int idx = threadIdx.x; idx < nh * D; idx += blockDim.x) {
         const int hh = idx / D;
@@ -478,45 +449,28 @@ attn_combine_kernel(const AttnParams p, int D) {
         float a = 0.0f, l = 0.0f;
         for (int s = 0; s < n_splits; ++s) {
             a += base[s * rec_floats + hh * D + d];
-            l += base[s * rec_floats + R * D + hh];
+            l += base[s * rec_floats + kHeads * D + hh];
         }
         const float val = n_splits > 0 ? a / l : 0.0f;
         store_out(p.out, p.out_dtype, t * p.so_t + n * p.so_n + (h0 + hh) * p.so_h + d, val);
     }
 }
 
-template <int W, int R, int NW>
-int launch_attn_nw(const AttnParams& p, bool vec, cudaStream_t stream) {
+template <int W>
+int launch_attn(const AttnParams& p, bool vec, cudaStream_t stream) {
     const int64_t blocks = p.items;
     if (blocks > 0x7fffffffLL) return SPK_ERR_TOO_LARGE;
     if (vec && (W == 2 || W == 4))
-        attn_decode_kernel<W, R, true, NW><<<static_cast<unsigned>(blocks), 32 * NW, 0, stream>>>(p);
+        attn_decode_kernel<W, true><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(p);
     else
-        attn_decode_kernel<W, R, false, NW><<<static_cast<unsigned>(blocks), 32 * NW, 0, stream>>>(p);
+        attn_decode_kernel<W, false><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(p);
     SPK_CHECK_LAUNCH();
     if (p.splits > 1) {
         const int64_t groups = p.items / p.splits;
-        attn_combine_kernel<R><<<static_cast<unsigned>(groups), 128, 0, stream>>>(p, 32 * W);
+        attn_combine_kernel<<<static_cast<unsigned>(groups), 128, 0, stream>>>(p, 32 * W);
         SPK_CHECK_LAUNCH();
     }
     return SPK_OK;
-}
-
-template <int W, int R>
-int launch_attn(const AttnParams& p, bool vec, cudaStream_t stream) {
-    return p.granule == 64 ? launch_attn_nw<W, R, 2>(p, vec, stream) : launch_attn_nw<W, R, 4>(p, vec, stream);
-}
-
-template <int W>
-int dispatch_r(const AttnParams& p, int R, bool vec, cudaStream_t stream) {
-    switch (R) {
-        case 1: return launch_attn<W, 1>(p, vec, stream);
-        case 2: return launch_attn<W, 2>(p, vec, stream);
-        case 4: return launch_attn<W, 4>(p, vec, stream);
-        case 7: return launch_attn<W, 7>(p, vec, stream);
-        case 8: return launch_attn<W, 8>(p, vec, stream);
-        default: return SPK_ERR_UNSUPPORTED;
-    }
 }
 
 static inline int log2_exact(int x) {
@@ -624,6 +578,8 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
     const int bs_log2 = log2_exact(block_size);
     if (bs_log2 < 0) return SPK_ERR_UNSUPPORTED;
     if (out_dtype != SPK_F32 && out_dtype != SPK_BF16 && out_dtype != SPK_F16) return SPK_ERR_BAD_DTYPE;
+    // the fp16 weight pairs cover exp(-24)..1 of the bound; head_dim^-0.5 (the reference's scale) gives <= 11.4
+    if (!(scale >= 0.0f) || scale * static_cast<float>(head_dim) > kMaxExponentRange) return SPK_ERR_UNSUPPORTED;
     if (T == 0 || n_seqs == 0) return SPK_OK;
     if (q == nullptr || k == nullptr || v == nullptr || block_tables == nullptr ||
         seq_lens == nullptr || out == nullptr)
@@ -643,7 +599,7 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
     p.T = T; p.n_seqs = n_seqs; p.Hq = num_q_heads; p.Hkv = num_kv_heads;
     p.n_rep = num_q_heads / num_kv_heads; p.passes = pl.passes;
     p.bs_log2 = bs_log2; p.max_blocks = max_blocks; p.num_blocks = num_blocks;
-    p.scale = scale; p.ws = static_cast<float*>(workspace); p.splits = pl.splits; p.granule = 32 * pl.warps;
+    p.scale = scale; p.ws = static_cast<float*>(workspace); p.splits = pl.splits;
     p.status = status;
     p.items = n_seqs * T * num_kv_heads * pl.passes * pl.splits;
 
@@ -651,10 +607,10 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
     const bool vec = aligned_to(k, sk_t, sk_h, sk_blk, sk_slot, W) && aligned_to(v, sv_t, sv_h, sv_blk, sv_slot, W);
     cudaStream_t s = spk_stream(stream);
     switch (W) {
-        case 1: return dispatch_r<1>(p, pl.R, vec, s);
-        case 2: return dispatch_r<2>(p, pl.R, vec, s);
-        case 3: return dispatch_r<3>(p, pl.R, vec, s);
-        case 4: return dispatch_r<4>(p, pl.R, vec, s);
+        case 1: return launch_attn<1>(p, vec, s);
+        case 2: return launch_attn<2>(p, vec, s);
+        case 3: return launch_attn<3>(p, vec, s);
+        case 4: return launch_attn<4>(p, vec, s);
         default: return SPK_ERR_UNSUPPORTED;
     }
 }

@@ -55,13 +55,19 @@ def test_host_side_argument_checks(lib):
     assert lib.spk_attn_decode(*args(48, 16)) == -6
     assert lib.spk_attn_decode(*args(64, 12)) == -6
     assert lib.spk_attn_decode(*args(256, 16)) == -6
-    # split-KV plan: a short table needs no workspace, BASELINE config 2 (64 x 4096 keys) does
+    # split-KV plan: rows are cut into key ranges only while the batch alone leaves SMs idle.  64 sequences
+    # (BASELINE config 2) fill the GPU: no workspace, no combine launch.  8 sequences x 4096 keys are cut.
     assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 1) == 0
-    ws = lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 256)
-    assert ws == 64 * 4 * 2 * 8 * (7 * 64 + 8) * 4
+    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 256) == 0
+    ws = lib.spk_attn_decode_workspace_bytes(4, 8, 14, 2, 64, 16, 256)
+    record = (8 * 64 + 8) * 4                    # eight heads x 64 sums + 8 totals, fp32
+    assert ws > 0 and ws % (8 * 4 * 2 * record) == 0
     assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 48, 16, 256) == 0
     # workspace required but missing -> rejected on the host, nothing launched
     big = (1, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 1, 1, _lib.F32, 0, 0, 0,
-           4, 64, 14, 2, 64, 16, 256, 8, 0.125, None, 0, None, None)
+           4, 8, 14, 2, 64, 16, 256, 8, 0.125, None, 0, None, None)
     assert lib.spk_attn_decode(*big) == -5
+    # a softmax range the fp16 weight pairs cannot hold (head_dim * scale > 24) is refused
+    wide = big[:-5] + (1.0, None, 0, None, None)
+    assert lib.spk_attn_decode(*wide) == -6
     assert lib.spk_meta_advance(1, 1, 1, 1, 1, 1, 1, 1, None, 2048, 4, 0, 16, None, None) == -2
