@@ -229,8 +229,8 @@ def attention_roofline(device, n_pools: int = 24, iters: int = 10) -> dict:
             "frac": round(achieved / peak, 4), "peak_source": f"of {which}",
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this case under ncu
             # (profiles/attn_decode_config2.md)
-            "traffic": 18.12e6,
-            "kernel": "attn_decode_kernel<W=2,R=7> (+ attn_combine_kernel)",
+            "traffic": 18.08e6,
+            "kernel": "attn_decode_kernel<W=2,VEC,NW=8> (fp16 m16n8k16 MMAs; one key range per row, no combine launch)",
             "workload": "64 seqs ragged [128,4096] (sum %d keys), 14/2 heads, D64, T4, p=0.2, page 16, bf16 out, "
                         "%d distinct pools back to back" % (sum_len, n_pools),
             "us_per_launch": round(us, 2), "algorithmic_bytes": alg}

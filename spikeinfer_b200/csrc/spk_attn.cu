@@ -21,34 +21,28 @@
 //        row is moved into the low byte of a half-word and all bits but one are masked off; what is
 //        left is either 0 or the fp16 subnormal 2^(i-24) for bit i.  Products with it are exact, and
 //        the known power of two is removed from the accumulators once, after the last key;
-//      - an extra all-ones column block yields the softmax denominators from the same MMAs.
-//    One 32-key tile of a 64-channel head costs 18 MMAs and about 200 instructions per warp, against
-//    about 620 instructions for the same tile as fp32 bit-selected adds on the SIMT pipes.
+//    The softmax denominators are plain fp32 sums of the same weights (a second table lookup per key).
+//    One 32-key tile of a 64-channel head costs 16 MMAs and about 250 instructions per warp, against
+//    about 620 instructions for the same tile as fp32 bit-selected adds on the SIMT pipes.  The
+//    register-fragment MMA path is the limit now (its pipe is busy ~80 % of the active cycles).
 #include "spk_common.cuh"
 
 namespace {
 
-#ifndef SPK_ATTN_WARPS
-#define SPK_ATTN_WARPS 4
-#endif
-constexpr int kWarps = SPK_ATTN_WARPS;  // warps per CTA
-constexpr int kThreads = 32 * kWarps;
-constexpr int kGranule = 32 * kWarps;  // keys per CTA step: one 32-key tile per warp
 constexpr int kHeads = 8;             // query heads per pass: rows 0..7 (hi) and 8..15 (lo) of the MMA tile
 constexpr int kMaxSplits = 256;
 #ifndef SPK_ATTN_CHUNK_MAX
 #define SPK_ATTN_CHUNK_MAX 4096
 #endif
-#ifndef SPK_ATTN_MIN_BLOCKS
-#define SPK_ATTN_MIN_BLOCKS (16 / SPK_ATTN_WARPS)  // 128 registers: sixteen warps per SM
+#ifndef SPK_ATTN_WIDE_CTA_KEYS
+#define SPK_ATTN_WIDE_CTA_KEYS 2048
 #endif
-#ifndef SPK_ATTN_TARGET_CTAS
-#define SPK_ATTN_TARGET_CTAS (148 * 3)
-#endif
+constexpr int kSmWarps = 16;  // resident warps per SM: the kernel is held to 128 registers
 // Weights are kept multiplied by 2^kScaleLog2: the largest (score = bound) is 2^14, inside the fp16
 // range, and the fp16 pair stays accurate down to exp(-24) of it.
 constexpr int kScaleLog2 = 14;
 constexpr float kMaxExponentRange = 24.0f;  // head_dim * scale above this is refused
+constexpr int kLutStride = 2 * 129 + 6;       // words between the fp16-pair tables and their fp32 twins
 constexpr float kLoUnscale = 1.0f / 2048.0f;  // the lo half of a weight is stored times 2^11
 
 struct AttnParams {
@@ -61,51 +55,65 @@ struct AttnParams {
     int T; int64_t n_seqs; int Hq, Hkv, n_rep, passes;
     int bs_log2; int64_t max_blocks, num_blocks;
     float scale;
-    float* ws; int splits;
+    float* ws; int splits; int granule;  // granule: keys per CTA step = 32 x warps per CTA
     uint32_t* status;
     int64_t items;
 };
 
 struct Plan {
     int passes;   // passes per KV head (eight query heads each)
+    int warps;    // warps per CTA: 4, or 8 for a single wave of long rows
     int splits;   // key ranges per sequence
     int chunk;    // keys per range (multiple of the granule)
     int64_t rec;  // floats per partial record
 };
+
+// A range is a whole number of granules (one 32-key tile per warp of the CTA).  Rows are cut only as far
+// as needed to fill the GPU once, and never into ranges above SPK_ATTN_CHUNK_MAX keys; when every row
+// fits one range the kernel writes the output itself and no combine launch follows.
+static inline void plan_ranges(Plan& p, int64_t base_items, int64_t max_keys) {
+    const int granule = 32 * p.warps;
+    const int64_t target = 148 * (kSmWarps / p.warps);
+    int64_t want = base_items > 0 ? target / base_items : 1;  // cut only while that still fits one wave
+    if (want < 1) want = 1;
+    int64_t chunk = (max_keys + want - 1) / want;
+    chunk = ((chunk + granule - 1) / granule) * granule;
+    if (chunk > SPK_ATTN_CHUNK_MAX) chunk = SPK_ATTN_CHUNK_MAX;
+    int64_t splits = (max_keys + chunk - 1) / chunk;
+    if (splits > kMaxSplits) {
+        splits = kMaxSplits;
+        chunk = (((max_keys + splits - 1) / splits + granule - 1) / granule) * granule;
+        splits = (max_keys + chunk - 1) / chunk;
+    }
+    if (splits < 1) splits = 1;
+    p.splits = static_cast<int>(splits);
+    p.chunk = static_cast<int>(chunk);
+}
 
 static inline Plan make_plan(int T, int64_t n_seqs, int Hq, int Hkv, int head_dim, int block_size,
                              int64_t max_blocks) {
     Plan p;
     const int n_rep = Hq / Hkv;
     p.passes = (n_rep + kHeads - 1) / kHeads;
-    // A range is a whole number of granules.  Rows are cut only as far as needed to fill the GPU once,
-    // and never into ranges above SPK_ATTN_CHUNK_MAX keys; when every row fits one range the kernel
-    // writes the output itself and no combine launch follows.
     const int64_t max_keys = max_blocks * block_size;
     const int64_t base_items = n_seqs * T * Hkv * p.passes;
-    int64_t want = base_items > 0 ? (SPK_ATTN_TARGET_CTAS + base_items - 1) / base_items : 1;
-    if (want < 1) want = 1;
-    int64_t chunk = (max_keys + want - 1) / want;
-    chunk = ((chunk + kGranule - 1) / kGranule) * kGranule;
-    if (chunk > SPK_ATTN_CHUNK_MAX) chunk = SPK_ATTN_CHUNK_MAX;
-    int64_t splits = (max_keys + chunk - 1) / chunk;
-    if (splits > kMaxSplits) {
-        splits = kMaxSplits;
-        chunk = (((max_keys + splits - 1) / splits + kGranule - 1) / kGranule) * kGranule;
-        splits = (max_keys + chunk - 1) / chunk;
+    p.warps = 4;
+    plan_ranges(p, base_items, max_keys);
+    // Long rows whose CTAs are all resident at once: the longest row sets the duration, so give every
+    // row eight warps (measured at 64 ragged rows of up to 4096 keys: 24.6 us against 26.7 us).
+    if (max_keys >= SPK_ATTN_WIDE_CTA_KEYS && base_items * p.splits <= 148 * (kSmWarps / 4)) {
+        p.warps = 8;
+        plan_ranges(p, base_items, max_keys);
     }
-    if (splits < 1) splits = 1;
-    p.splits = static_cast<int>(splits);
-    p.chunk = static_cast<int>(chunk);
     p.rec = static_cast<int64_t>(kHeads) * head_dim + 8;  // 8*D sums, then the 8 weight totals
     return p;
 }
 
 // Keys per range of a row of `len` keys cut into at most `splits` ranges of whole granules.
-__device__ __forceinline__ int64_t row_range_keys(int64_t len, int splits) {
-    const int64_t gr = (len + kGranule - 1) / kGranule;
+__device__ __forceinline__ int64_t row_range_keys(int64_t len, int splits, int granule) {
+    const int64_t gr = (len + granule - 1) / granule;
     const int64_t n = gr < splits ? (gr > 0 ? gr : 1) : splits;
-    return ((gr + n - 1) / n) * kGranule;
+    return ((gr + n - 1) / n) * granule;
 }
 
 __device__ __forceinline__ void store_out(void* out, int dtype, int64_t idx, float v) {
@@ -184,7 +192,7 @@ __device__ __forceinline__ void load_pair(const uint32_t* p, uint32_t (&r0)[W], 
 template <int W, bool ALL>
 __device__ __forceinline__ void tile_mma(const uint32_t* kst, const uint32_t* vst, const uint32_t (&qw)[W],
                                          const uint32_t* my_lut, const uint32_t* zero_lut, unsigned live,
-                                         int gid, int tig, float (&acc)[4 * W][4], float (&accl)[4]) {
+                                         int gid, int tig, float (&acc)[4 * W][4], float& lsum) {
     const uint32_t gmask = (1u << gid) | (1u << (16 + gid));  // bit gid of both half-words
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks) {
@@ -205,6 +213,7 @@ __device__ __forceinline__ void tile_mma(const uint32_t* kst, const uint32_t* vs
             const int key = k0 + (i & 1) + 8 * (i >> 1);
             const uint32_t* tab = (ALL || ((live >> key) & 1u)) ? my_lut : zero_lut;
             wt[i] = tab[-s];
+            lsum += __uint_as_float(tab[kLutStride - s]);  // the same weight in fp32, for the denominator
         }
         uint32_t a[4];
         a[0] = prmt(wt[0], wt[1], 0x5410);  // hi(k0), hi(k0+1)      -> row gid
@@ -220,21 +229,24 @@ __device__ __forceinline__ void tile_mma(const uint32_t* kst, const uint32_t* vs
             const uint32_t sel = b | (b << 4) | ((4u + b) << 8) | ((4u + b) << 12);
             mma16816(acc[j], a, prmt(vw[0][w], vw[1][w], sel) & gmask, prmt(vw[2][w], vw[3][w], sel) & gmask);
         }
-        mma16816(accl, a, 0x3C003C00u, 0x3C003C00u);  // ones: the weight totals
     }
 }
 
-template <int W, bool VEC>
-__global__ void __launch_bounds__(kThreads, SPK_ATTN_MIN_BLOCKS)
+template <int W, bool VEC, int NW>
+__global__ void __launch_bounds__(32 * NW, kSmWarps / NW)
 attn_decode_kernel(const AttnParams p) {
+    constexpr int kWarps = NW;
+    constexpr int kThreads = 32 * NW;
+    constexpr int kGranule = 32 * NW;  // keys per CTA step
     constexpr int D = 32 * W;
     constexpr int LUTN = D + 1;
     constexpr int REC = kHeads * D + 8;  // 8*D sums, then the 8 weight totals
     __shared__ __align__(16) uint32_t kst_all[kWarps][32 * W];
     __shared__ __align__(16) uint32_t vst_all[kWarps][32 * W];
-    // weight table ({hi, lo} fp16 pairs, indexed by bound - score) and an all-zero one for dead keys
-    // and absent heads
-    __shared__ uint32_t lut[2 * LUTN];
+    // weight tables indexed by bound - score: {hi, lo} fp16 pairs, then (kLutStride words on) the same
+    // weights in fp32; an all-zero copy of both for dead keys and absent heads sits LUTN words further
+    static_assert(2 * LUTN <= kLutStride, "table stride");
+    __shared__ uint32_t lut[2 * kLutStride];
     // per-warp partial sums, folded at the end; head rows padded by 8 floats against bank conflicts
     constexpr int RS = D + 8;
     __shared__ __align__(16) float red[kWarps][kHeads * RS + 8];
@@ -304,7 +316,7 @@ attn_decode_kernel(const AttnParams p) {
     }
     // A row is cut into up to `splits` equal key ranges of whole granules, whatever its length: short
     // rows are spread over several CTAs too (short critical path when the GPU is underfilled).
-    const int64_t range = row_range_keys(len, p.splits);
+    const int64_t range = row_range_keys(len, p.splits, p.granule);
     const int64_t begin = static_cast<int64_t>(c) * range;
     if (begin >= len && !(len == 0 && c == 0 && p.splits == 1)) return;
     const int64_t end = min(len, begin + range);
@@ -321,10 +333,9 @@ attn_decode_kernel(const AttnParams p) {
         qw[w] = gid < nh ? __ldg(p.q + t * p.sq_t + n * p.sq_n + (h0 + gid) * p.sq_h + w) : 0u;
         cmax += __popc(qw[w]);
     }
-    float acc[4 * W][4], accl[4];
+    float acc[4 * W][4], lsum = 0.0f;
 #pragma unroll
     for (int j = 0; j < 4 * W; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
-    accl[0] = accl[1] = accl[2] = accl[3] = 0.0f;
 
     const uint32_t* kbase = p.k + t * p.sk_t + g * p.sk_h;
     const uint32_t* vbase = p.v + t * p.sv_t + g * p.sv_h;
@@ -355,14 +366,16 @@ attn_decode_kernel(const AttnParams p) {
     // A weight depends on bound - score only: lut[d] = {hi, lo} with hi + lo * 2^-11 =
     // 2^kScaleLog2 * exp(-d * scale), d = 0..head_dim, shared by all heads.
     for (int i = threadIdx.x; i < 2 * LUTN; i += kThreads) {
-        uint32_t e = 0u;
+        uint32_t e = 0u, f = 0u;
         if (i < LUTN) {
             const float wv = ldexpf(expf(-static_cast<float>(i) * p.scale), kScaleLog2);
             const __half hi = __float2half_rn(wv);
             const __half lo = __float2half_rn((wv - __half2float(hi)) * 2048.0f);
             e = static_cast<uint32_t>(__half_as_ushort(hi)) | (static_cast<uint32_t>(__half_as_ushort(lo)) << 16);
+            f = __float_as_uint(wv);
         }
         lut[i] = e;
+        lut[kLutStride + i] = f;
     }
     __syncthreads();
     // tables are indexed with -score from these bases: live keys of a present head read lut[cmax - s],
@@ -380,8 +393,8 @@ attn_decode_kernel(const AttnParams p) {
         phys_b = phys_c;
         __syncwarp();
         // ---- weights and weighted sums on the tensor cores (lane = (head, key quad)) -----------------
-        if (live == 0xffffffffu) tile_mma<W, true>(kst, vst, qw, my_lut, zero_lut, live, gid, tig, acc, accl);
-        else tile_mma<W, false>(kst, vst, qw, my_lut, zero_lut, live, gid, tig, acc, accl);
+        if (live == 0xffffffffu) tile_mma<W, true>(kst, vst, qw, my_lut, zero_lut, live, gid, tig, acc, lsum);
+        else tile_mma<W, false>(kst, vst, qw, my_lut, zero_lut, live, gid, tig, acc, lsum);
         __syncwarp();
     }
 
@@ -396,7 +409,9 @@ attn_decode_kernel(const AttnParams p) {
         const float v1 = (acc[j][1] + acc[j][3] * kLoUnscale) * u1;
         *reinterpret_cast<float2*>(&red[warp][gid * RS + 8 * j + 2 * tig]) = make_float2(v0, v1);
     }
-    if (tig == 0) red[warp][kHeads * RS + gid] = accl[0] + accl[2] * kLoUnscale;
+    lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);  // the four threads of a head hold disjoint keys
+    lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+    if (tig == 0) red[warp][kHeads * RS + gid] = lsum;
     __syncthreads();
     if (p.splits == 1) {
         for (int idx = threadIdx.x; idx < nh * D; idx += kThreads) {
@@ -439,7 +454,7 @@ attn_combine_kernel(const AttnParams p, int D) {
     const int64_t max_keys = p.max_blocks << p.bs_log2;
     if (len < 1) len = 0;
     if (len > max_keys) len = max_keys;
-    const int64_t range = row_range_keys(len, p.splits);
+    const int64_t range = row_range_keys(len, p.splits, p.granule);
     const int n_splits = static_cast<int>((len + range - 1) / range);
     const int64_t rec_floats = static_cast<int64_t>(kHeads) * D + 8;
     const float* base = p.ws + grp_item * p.splits * rec_floats;
@@ -456,14 +471,14 @@ attn_combine_kernel(const AttnParams p, int D) {
     }
 }
 
-template <int W>
-int launch_attn(const AttnParams& p, bool vec, cudaStream_t stream) {
+template <int W, int NW>
+int launch_attn_nw(const AttnParams& p, bool vec, cudaStream_t stream) {
     const int64_t blocks = p.items;
     if (blocks > 0x7fffffffLL) return SPK_ERR_TOO_LARGE;
     if (vec && (W == 2 || W == 4))
-        attn_decode_kernel<W, true><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(p);
+        attn_decode_kernel<W, true, NW><<<static_cast<unsigned>(blocks), 32 * NW, 0, stream>>>(p);
     else
-        attn_decode_kernel<W, false><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(p);
+        attn_decode_kernel<W, false, NW><<<static_cast<unsigned>(blocks), 32 * NW, 0, stream>>>(p);
     SPK_CHECK_LAUNCH();
     if (p.splits > 1) {
         const int64_t groups = p.items / p.splits;
@@ -471,6 +486,11 @@ int launch_attn(const AttnParams& p, bool vec, cudaStream_t stream) {
         SPK_CHECK_LAUNCH();
     }
     return SPK_OK;
+}
+
+template <int W>
+int launch_attn(const AttnParams& p, bool vec, cudaStream_t stream) {
+    return p.granule == 256 ? launch_attn_nw<W, 8>(p, vec, stream) : launch_attn_nw<W, 4>(p, vec, stream);
 }
 
 static inline int log2_exact(int x) {
@@ -599,7 +619,7 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
     p.T = T; p.n_seqs = n_seqs; p.Hq = num_q_heads; p.Hkv = num_kv_heads;
     p.n_rep = num_q_heads / num_kv_heads; p.passes = pl.passes;
     p.bs_log2 = bs_log2; p.max_blocks = max_blocks; p.num_blocks = num_blocks;
-    p.scale = scale; p.ws = static_cast<float*>(workspace); p.splits = pl.splits;
+    p.scale = scale; p.ws = static_cast<float*>(workspace); p.splits = pl.splits; p.granule = 32 * pl.warps;
     p.status = status;
     p.items = n_seqs * T * num_kv_heads * pl.passes * pl.splits;
 

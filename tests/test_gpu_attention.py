@@ -196,3 +196,54 @@ def test_config2_full_size(dev):
     keys = ("q_packed", "k_cache", "block_tables", "seq_lens", "head_dim", "block_size", "num_q_heads", "num_kv_heads")
     sub = {k: (case[k][:, :4] if k == "q_packed" else case[k][:4] if k in ("block_tables", "seq_lens") else case[k]) for k in keys}
     assert torch.equal(kernels.qk_scores(**to_dev(sub, dev)).cpu(), orc.qk_scores(**sub))
+
+
+def attention_fp64(case):
+    """The same softmax-weighted sum in float64 from the unpacked bits: the yardstick for rows so long that the
+    fp32 oracle's own rounding (3.8e-5 at 32768 keys) is above the bar."""
+    D, Hq, Hkv = case["head_dim"], case["num_q_heads"], case["num_kv_heads"]
+    q = orc.unpack_spikes(case["q_packed"], D, torch.float64)  # [T, n, Hq, D]
+    out = torch.zeros(q.shape, dtype=torch.float64)
+    for n in range(q.shape[1]):
+        length = int(case["seq_lens"][n])
+        k = orc.gather_kv_unpacked(case["k_cache"], case["block_tables"][n], length, D, case["block_size"], torch.float64)
+        v = orc.gather_kv_unpacked(case["v_cache"], case["block_tables"][n], length, D, case["block_size"], torch.float64)
+        k = k.repeat_interleave(Hq // Hkv, dim=1)  # [T, Hq, L, D]
+        v = v.repeat_interleave(Hq // Hkv, dim=1)
+        s = torch.einsum("thd,thld->thl", q[:, n], k) * D ** -0.5
+        out[:, n] = torch.einsum("thl,thld->thd", torch.softmax(s, -1), v)
+    return out
+
+
+@pytest.mark.parametrize("seq_lens,max_blocks,density", [([32768], 2048, 0.2), ([9000, 2500], 1024, 0.5)])
+def test_long_rows_against_float64(seq_lens, max_blocks, density, dev):
+    """Accumulation over tens of thousands of keys (tensor-core sums, partial records, combine) stays within
+    2e-6 of an exact evaluation; the bf16 and fp32 bars of the short cases are met with room to spare."""
+    case = cases.attention_case(seq_lens=seq_lens, density=density, seed=5, spare_blocks=0, max_blocks=max_blocks)
+    got = run(case, dev).cpu().double()
+    want = attention_fp64(case)
+    err = ((got - want).abs().max() / want.abs().max()).item()
+    assert err < 2e-6, f"{err:.2e}"
+
+
+def test_softmax_range_beyond_the_weight_format_is_refused(dev):
+    """The library's weights cover exp(-24)..1 of the softmax bound (scale * head_dim <= 24); the reference's
+    scale, head_dim^-0.5, is far inside.  A wider range is rejected on the host, nothing is launched."""
+    lib = _lib.load()
+    case = to_dev(cases.attention_case(seq_lens=[40]), dev)
+    q, k, v, tables, lens = (case[n] for n in ("q_packed", "k_cache", "v_cache", "block_tables", "seq_lens"))
+    out = torch.full((q.shape[0], 1, case["num_q_heads"], 64), 7.0, device=dev)
+    args = [q.data_ptr(), q.stride(0), q.stride(1), q.stride(2),
+            k.data_ptr(), k.stride(0), k.stride(1), k.stride(2) * 16, k.stride(2),
+            v.data_ptr(), v.stride(0), v.stride(1), v.stride(2) * 16, v.stride(2),
+            tables.data_ptr(), tables.stride(0), lens.data_ptr(),
+            out.data_ptr(), _lib.F32, out.stride(0), out.stride(1), out.stride(2),
+            q.shape[0], 1, case["num_q_heads"], case["num_kv_heads"], 64, 16, tables.shape[1], k.shape[2] // 16]
+    tail = [None, 0, None, None]
+    assert lib.spk_attn_decode(*args, 0.5, *tail) == -6      # 64 * 0.5 = 32 > 24
+    assert lib.spk_attn_decode(*args, -0.1, *tail) == -6
+    torch.cuda.synchronize()
+    assert (out == 7.0).all()
+    assert lib.spk_attn_decode(*args, 0.125, *tail) == 0
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all() and not (out == 7.0).all()
