@@ -47,13 +47,13 @@ constexpr float kLoUnscale = 1.0f / 2048.0f;  // the lo half of a weight is stor
 
 struct AttnParams {
     const uint32_t* q; int64_t sq_t, sq_n, sq_h;
-    const uint32_t* k; int64_t sk_t, sk_h, sk_blk, sk_slot;
-    const uint32_t* v; int64_t sv_t, sv_h, sv_blk, sv_slot;
+    const uint32_t* k; int64_t sk_t, sk_h; int sk_blk, sk_slot;  // page and slot strides fit 31 bits (host-checked)
+    const uint32_t* v; int64_t sv_t, sv_h; int sv_blk, sv_slot;
     const int32_t* tables; int64_t sbt_n;
     const int32_t* lens;
     void* out; int out_dtype; int64_t so_t, so_n, so_h;
     int T; int64_t n_seqs; int Hq, Hkv, n_rep, passes;
-    int bs_log2; int64_t max_blocks, num_blocks;
+    int bs_log2; int max_keys, num_blocks;  // max_keys = max_blocks * block_size, below 2^31 (host-checked)
     float scale;
     float* ws; int splits; int granule;  // granule: keys per CTA step = 32 x warps per CTA
     uint32_t* status;
@@ -110,9 +110,9 @@ static inline Plan make_plan(int T, int64_t n_seqs, int Hq, int Hkv, int head_di
 }
 
 // Keys per range of a row of `len` keys cut into at most `splits` ranges of whole granules.
-__device__ __forceinline__ int64_t row_range_keys(int64_t len, int splits, int granule) {
-    const int64_t gr = (len + granule - 1) / granule;
-    const int64_t n = gr < splits ? (gr > 0 ? gr : 1) : splits;
+__device__ __forceinline__ int row_range_keys(int len, int splits, int granule) {
+    const int gr = (len + granule - 1) / granule;
+    const int n = gr < splits ? (gr > 0 ? gr : 1) : splits;
     return ((gr + n - 1) / n) * granule;
 }
 
@@ -142,18 +142,19 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
 // 8- or 16-byte access.
 template <int W, bool VEC>
 __device__ __forceinline__ void load_row(const uint32_t* p, bool ok, uint32_t (&r)[W]) {
-#pragma unroll
-    for (int w = 0; w < W; ++w) r[w] = 0;
-    if (!ok) return;
+    // (selects, not branches: the address is always a valid one, dead keys read slot 0 of page 0)
     if (VEC && W == 2) {
         const uint2 t = __ldg(reinterpret_cast<const uint2*>(p));
-        r[0] = t.x; r[1] = t.y;
+        r[0] = ok ? t.x : 0u; r[1] = ok ? t.y : 0u;
     } else if (VEC && W == 4) {
         const uint4 t = __ldg(reinterpret_cast<const uint4*>(p));
-        r[0] = t.x; r[1] = t.y; r[2] = t.z; r[3] = t.w;
+        r[0] = ok ? t.x : 0u; r[1] = ok ? t.y : 0u; r[2] = ok ? t.z : 0u; r[3] = ok ? t.w : 0u;
     } else {
 #pragma unroll
-        for (int w = 0; w < W; ++w) r[w] = __ldg(p + w);
+        for (int w = 0; w < W; ++w) {
+            const uint32_t t = __ldg(p + w);
+            r[w] = ok ? t : 0u;
+        }
     }
 }
 
@@ -269,9 +270,8 @@ attn_decode_kernel(const AttnParams p) {
         // ties by index, and this item serves the row of rank `rest`.  The long-running CTAs are thus
         // scheduled early and the last wave holds short rows.  Ballots over the lengths held one or a
         // few per lane: a few dozen instructions per warp.
-        const int64_t max_keys_ = p.max_blocks << p.bs_log2;
         int shift = 0;
-        while ((max_keys_ >> shift) > 8) ++shift;
+        while ((p.max_keys >> shift) > 8) ++shift;
         int cls[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -308,22 +308,21 @@ attn_decode_kernel(const AttnParams p) {
     const int h0 = g * p.n_rep + pass * kHeads;
     const int nh = min(kHeads, p.n_rep - pass * kHeads);
 
-    int64_t len = p.lens[n];
-    const int64_t max_keys = p.max_blocks << p.bs_log2;
-    if (len < 1 || len > max_keys) {
+    int len = p.lens[n];
+    if (len < 1 || len > p.max_keys) {
         if (threadIdx.x == 0 && c == 0) spk_flag(p.status, SPK_STATUS_BAD_SEQ_LEN);
-        len = len < 1 ? 0 : max_keys;
+        len = len < 1 ? 0 : p.max_keys;
     }
     // A row is cut into up to `splits` equal key ranges of whole granules, whatever its length: short
     // rows are spread over several CTAs too (short critical path when the GPU is underfilled).
-    const int64_t range = row_range_keys(len, p.splits, p.granule);
-    const int64_t begin = static_cast<int64_t>(c) * range;
+    const int range = row_range_keys(len, p.splits, p.granule);
+    const int begin = c * range;
     if (begin >= len && !(len == 0 && c == 0 && p.splits == 1)) return;
-    const int64_t end = min(len, begin + range);
+    const int end = min(len, begin + range);
 
     uint32_t* kst = kst_all[warp];
     uint32_t* vst = vst_all[warp];
-    const int64_t first = begin + 32 * warp;  // this warp's first tile; the next one is kGranule keys on
+    const int first = begin + 32 * warp;  // this warp's first tile; the next one is kGranule keys on
 
     // Query words of this thread's head and their popcount (the softmax bound).
     uint32_t qw[W];
@@ -344,18 +343,17 @@ attn_decode_kernel(const AttnParams p) {
 
     // Three-stage software pipeline over this warp's tiles: block-table entry of the tile after next,
     // K/V rows of the next tile (lane = key, coalesced), arithmetic of the current one.
-    auto table_entry = [&](int64_t key) -> int32_t {
+    auto table_entry = [&](int key) -> int32_t {
         return key < end ? __ldg(table + (key >> p.bs_log2)) : -1;
     };
-    auto fetch = [&](int64_t key, int32_t phys, uint32_t (&kr)[W], uint32_t (&vr)[W]) -> bool {
-        bool ok = key < end;
-        if (ok && (phys < 0 || phys >= p.num_blocks)) {
-            spk_flag(p.status, SPK_STATUS_BAD_BLOCK);
-            ok = false;
-        }
-        const int64_t slot = key & bs_mask;
-        load_row<W, VEC>(kbase + static_cast<int64_t>(phys) * p.sk_blk + slot * p.sk_slot, ok, kr);
-        load_row<W, VEC>(vbase + static_cast<int64_t>(phys) * p.sv_blk + slot * p.sv_slot, ok, vr);
+    auto fetch = [&](int key, int32_t phys, uint32_t (&kr)[W], uint32_t (&vr)[W]) -> bool {
+        const bool in_range = key < end;
+        const bool ok = in_range && static_cast<uint32_t>(phys) < static_cast<uint32_t>(p.num_blocks);
+        if (in_range && !ok) spk_flag(p.status, SPK_STATUS_BAD_BLOCK);
+        const int page = ok ? phys : 0;
+        const int slot = ok ? (key & bs_mask) : 0;
+        load_row<W, VEC>(kbase + static_cast<int64_t>(page) * p.sk_blk + slot * p.sk_slot, ok, kr);
+        load_row<W, VEC>(vbase + static_cast<int64_t>(page) * p.sv_blk + slot * p.sv_slot, ok, vr);
         return ok;
     };
     int32_t phys_b = table_entry(first + kGranule + lane);  // this warp's second tile
@@ -383,7 +381,7 @@ attn_decode_kernel(const AttnParams p) {
     const uint32_t* zero_lut = lut + LUTN + cmax;
     const uint32_t* my_lut = gid < nh ? lut + cmax : zero_lut;
 
-    for (int64_t tile = first; tile < end; tile += kGranule) {
+    for (int tile = first; tile < end; tile += kGranule) {
         // ---- stage the current tile (lane = key) and start the next one's loads --------------------
         store_row<W>(kst + lane * W, kn);
         store_row<W>(vst + lane * W, vn);
@@ -450,11 +448,10 @@ attn_combine_kernel(const AttnParams p, int D) {
     const int h0 = g * p.n_rep + pass * kHeads;
     const int nh = min(kHeads, p.n_rep - pass * kHeads);
 
-    int64_t len = p.lens[n];
-    const int64_t max_keys = p.max_blocks << p.bs_log2;
+    int len = p.lens[n];
     if (len < 1) len = 0;
-    if (len > max_keys) len = max_keys;
-    const int64_t range = row_range_keys(len, p.splits, p.granule);
+    if (len > p.max_keys) len = p.max_keys;
+    const int range = row_range_keys(len, p.splits, p.granule);
     const int n_splits = static_cast<int>((len + range - 1) / range);
     const int64_t rec_floats = static_cast<int64_t>(kHeads) * D + 8;
     const float* base = p.ws + grp_item * p.splits * rec_floats;
@@ -605,6 +602,12 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
         seq_lens == nullptr || out == nullptr)
         return SPK_ERR_NULL_POINTER;
 
+    // the kernel indexes keys, pages and the page/slot strides with 32-bit integers
+    const int64_t lim = 0x7fffffffLL;
+    if (max_blocks > (lim >> bs_log2) - 8 || num_blocks > lim) return SPK_ERR_TOO_LARGE;
+    for (int64_t st : {sk_blk, sk_slot, sv_blk, sv_slot})
+        if (st > lim || st < -lim) return SPK_ERR_TOO_LARGE;
+
     const Plan pl = make_plan(T, n_seqs, num_q_heads, num_kv_heads, head_dim, block_size, max_blocks);
     const int64_t need = pl.splits == 1 ? 0
         : n_seqs * T * num_kv_heads * pl.passes * pl.splits * pl.rec * static_cast<int64_t>(sizeof(float));
@@ -612,13 +615,13 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
 
     AttnParams p;
     p.q = reinterpret_cast<const uint32_t*>(q); p.sq_t = sq_t; p.sq_n = sq_n; p.sq_h = sq_h;
-    p.k = reinterpret_cast<const uint32_t*>(k); p.sk_t = sk_t; p.sk_h = sk_h; p.sk_blk = sk_blk; p.sk_slot = sk_slot;
-    p.v = reinterpret_cast<const uint32_t*>(v); p.sv_t = sv_t; p.sv_h = sv_h; p.sv_blk = sv_blk; p.sv_slot = sv_slot;
+    p.k = reinterpret_cast<const uint32_t*>(k); p.sk_t = sk_t; p.sk_h = sk_h; p.sk_blk = static_cast<int>(sk_blk); p.sk_slot = static_cast<int>(sk_slot);
+    p.v = reinterpret_cast<const uint32_t*>(v); p.sv_t = sv_t; p.sv_h = sv_h; p.sv_blk = static_cast<int>(sv_blk); p.sv_slot = static_cast<int>(sv_slot);
     p.tables = block_tables; p.sbt_n = sbt_n; p.lens = seq_lens;
     p.out = out; p.out_dtype = out_dtype; p.so_t = so_t; p.so_n = so_n; p.so_h = so_h;
     p.T = T; p.n_seqs = n_seqs; p.Hq = num_q_heads; p.Hkv = num_kv_heads;
     p.n_rep = num_q_heads / num_kv_heads; p.passes = pl.passes;
-    p.bs_log2 = bs_log2; p.max_blocks = max_blocks; p.num_blocks = num_blocks;
+    p.bs_log2 = bs_log2; p.max_keys = static_cast<int>(max_blocks << bs_log2); p.num_blocks = static_cast<int>(num_blocks);
     p.scale = scale; p.ws = static_cast<float*>(workspace); p.splits = pl.splits; p.granule = 32 * pl.warps;
     p.status = status;
     p.items = n_seqs * T * num_kv_heads * pl.passes * pl.splits;
