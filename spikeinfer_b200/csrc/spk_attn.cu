@@ -17,8 +17,8 @@
 //      - left operand: the weight of (head, key), split into two fp16 numbers hi + lo * 2^-11 that
 //        occupy rows h and h + 8 of the 16-row tile (22 significant bits together; the table holds
 //        the pair ready-made);
-//      - right operand: the V bit of (key, channel) used IN PLACE as an fp16 number.  A byte of the V
-//        row is moved into the low byte of a half-word and all bits but one are masked off; what is
+//      - right operand: the V bit of (key, channel) used IN PLACE as an fp16 number.  The V rows of two
+//        consecutive keys are staged interleaved by half-word and all bits but one are masked off; what is
 //        left is either 0 or the fp16 subnormal 2^(i-24) for bit i.  Products with it are exact, and
 //        the known power of two is removed from the accumulators once, after the last key;
 //    The softmax denominators are plain fp32 sums of the same weights (a second table lookup per key).
@@ -37,7 +37,10 @@ constexpr int kMaxSplits = 256;
 #ifndef SPK_ATTN_WIDE_CTA_KEYS
 #define SPK_ATTN_WIDE_CTA_KEYS 2048
 #endif
-constexpr int kSmWarps = 16;  // resident warps per SM: the kernel is held to 128 registers
+#ifndef SPK_ATTN_SM_WARPS
+#define SPK_ATTN_SM_WARPS 16
+#endif
+constexpr int kSmWarps = SPK_ATTN_SM_WARPS;  // resident warps per SM: the kernel is held to 128 registers
 // Weights are kept multiplied by 2^kScaleLog2: the largest (score = bound) is 2^14, inside the fp16
 // range, and the fp16 pair stays accurate down to exp(-24) of it.
 constexpr int kScaleLog2 = 14;
@@ -101,7 +104,8 @@ static inline Plan make_plan(int T, int64_t n_seqs, int Hq, int Hkv, int head_di
     plan_ranges(p, base_items, max_keys);
     // Long rows whose CTAs are all resident at once: the longest row sets the duration, so give every
     // row eight warps (measured at 64 ragged rows of up to 4096 keys: 24.6 us against 26.7 us).
-    if (max_keys >= SPK_ATTN_WIDE_CTA_KEYS && base_items * p.splits <= 148 * (kSmWarps / 4)) {
+    // (head_dim 128: the eight partial-sum buffers would not fit the static shared memory)
+    if (head_dim <= 96 && max_keys >= SPK_ATTN_WIDE_CTA_KEYS && base_items * p.splits <= 148 * (kSmWarps / 4)) {
         p.warps = 8;
         plan_ranges(p, base_items, max_keys);
     }
@@ -169,20 +173,47 @@ __device__ __forceinline__ void store_row(uint32_t* p, const uint32_t (&r)[W]) {
     }
 }
 
-// Two adjacent staged rows (keys k and k + 1, k even): 2W consecutive words, 8W-byte aligned.
-template <int W>
-__device__ __forceinline__ void load_pair(const uint32_t* p, uint32_t (&r0)[W], uint32_t (&r1)[W]) {
-    if (W == 1) {
-        const uint2 t = *reinterpret_cast<const uint2*>(p);
-        r0[0] = t.x; r1[0] = t.y;
-    } else if (W == 2) {
-        const uint4 t = *reinterpret_cast<const uint4*>(p);
-        r0[0] = t.x; r0[1] = t.y; r1[0] = t.z; r1[1] = t.w;
+// N consecutive staged words, 4N-byte aligned when N is a power of two and 8-byte aligned otherwise
+// (the rows of a key pair).
+template <int N>
+__device__ __forceinline__ void load_words(const uint32_t* p, uint32_t (&r)[N]) {
+    if (N % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < N / 4; ++i) {
+            const uint4 t = reinterpret_cast<const uint4*>(p)[i];
+            r[4 * i] = t.x; r[4 * i + 1] = t.y; r[4 * i + 2] = t.z; r[4 * i + 3] = t.w;
+        }
     } else {
 #pragma unroll
-        for (int w = 0; w < W; ++w) { r0[w] = p[w]; r1[w] = p[W + w]; }
+        for (int i = 0; i < N / 2; ++i) {
+            const uint2 t = reinterpret_cast<const uint2*>(p)[i];
+            r[2 * i] = t.x; r[2 * i + 1] = t.y;
+        }
     }
 }
+
+// V bits as fp16 numbers.  The V rows of a key pair (k, k + 1) are staged interleaved by half-word:
+// word h of the pair holds bits 16h..16h+15 of key k in its low half and of key k + 1 in its high half,
+// which is the register layout of the MMA's right operand (two consecutive keys, one channel).  Masking
+// one bit per half leaves 0 or a power of two:
+//   bits 0..9 are fp16 mantissa bits: 2^(b-24) (subnormal); bits 10..14 exponent bits: 2^(2^(b-10) - 15);
+//   bit 15 is the sign and unusable, so the threads of column 7 (gid 7) read a second copy of the staging
+//   in which every half-word is shifted right by one, and mask bits 6 and 14 instead of 7 and 15.
+// The power of two depends only on (column, byte parity) and is removed from the accumulators at the end.
+struct VBits {
+    __device__ static __forceinline__ int bit(int col, int odd_byte) {
+        return col == 7 ? (odd_byte ? 14 : 6) : col + 8 * odd_byte;
+    }
+    __device__ static __forceinline__ uint32_t mask(int col, int odd_byte) {
+        const uint32_t b = 1u << bit(col, odd_byte);
+        return b | (b << 16);
+    }
+    // log2 of the fp16 value of that single bit
+    __device__ static __forceinline__ int log2_value(int col, int odd_byte) {
+        const int b = bit(col, odd_byte);
+        return b < 10 ? b - 24 : (1 << (b - 10)) - 15;
+    }
+};
 
 // One 32-key tile of a warp, from the staged K and V rows.  ALL: every key of the tile is live
 // (`live` is all ones); otherwise keys whose bit in `live` is clear get weight zero.
@@ -194,23 +225,24 @@ template <int W, bool ALL>
 __device__ __forceinline__ void tile_mma(const uint32_t* kst, const uint32_t* vst, const uint32_t (&qw)[W],
                                          const uint32_t* my_lut, const uint32_t* zero_lut, unsigned live,
                                          int gid, int tig, float (&acc)[4 * W][4], float& lsum) {
-    const uint32_t gmask = (1u << gid) | (1u << (16 + gid));  // bit gid of both half-words
+    // Bit kept from each half-word for the even / odd byte of a half-word (see VBits below).
+    const uint32_t m0 = VBits::mask(gid, 0), m1 = VBits::mask(gid, 1);
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks) {
         // this thread's keys of the 16-key step: k0, k0 + 1, k0 + 8, k0 + 9
         const int k0 = 16 * ks + 2 * tig;
-        uint32_t kw[4][W], vw[4][W];
-        load_pair<W>(kst + k0 * W, kw[0], kw[1]);
-        load_pair<W>(kst + (k0 + 8) * W, kw[2], kw[3]);
-        load_pair<W>(vst + k0 * W, vw[0], vw[1]);
-        load_pair<W>(vst + (k0 + 8) * W, vw[2], vw[3]);
+        uint32_t kw[2][2 * W], vx[2][2 * W];  // [key pair][words]: K rows of the two keys; interleaved V
+        load_words<2 * W>(kst + k0 * W, kw[0]);
+        load_words<2 * W>(kst + (k0 + 8) * W, kw[1]);
+        load_words<2 * W>(vst + k0 * W, vx[0]);
+        load_words<2 * W>(vst + (k0 + 8) * W, vx[1]);
         // weights of (head gid, these keys): {hi, lo} fp16 pairs from the table, indexed by bound - score
         uint32_t wt[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             int s = 0;
 #pragma unroll
-            for (int w = 0; w < W; ++w) s += __popc(qw[w] & kw[i][w]);
+            for (int w = 0; w < W; ++w) s += __popc(qw[w] & kw[i >> 1][(i & 1) * W + w]);
             const int key = k0 + (i & 1) + 8 * (i >> 1);
             const uint32_t* tab = (ALL || ((live >> key) & 1u)) ? my_lut : zero_lut;
             wt[i] = tab[-s];
@@ -221,14 +253,12 @@ __device__ __forceinline__ void tile_mma(const uint32_t* kst, const uint32_t* vs
         a[1] = prmt(wt[0], wt[1], 0x7632);  // lo(k0), lo(k0+1)      -> row gid + 8
         a[2] = prmt(wt[2], wt[3], 0x5410);  // hi(k0+8), hi(k0+9)
         a[3] = prmt(wt[2], wt[3], 0x7632);
-        // V bits of channel 8j + gid for the same keys, as fp16: byte (j % 4) of word j / 4 goes to the
-        // low byte of each half-word, then everything but bit gid is masked off.
+        // V bits of channel 8j + gid for the same keys, as fp16: half-word pair j / 2 of each key pair,
+        // all bits but this thread's one masked off.
 #pragma unroll
         for (int j = 0; j < 4 * W; ++j) {
-            const int w = j >> 2;
-            const uint32_t b = j & 3;
-            const uint32_t sel = b | (b << 4) | ((4u + b) << 8) | ((4u + b) << 12);
-            mma16816(acc[j], a, prmt(vw[0][w], vw[1][w], sel) & gmask, prmt(vw[2][w], vw[3][w], sel) & gmask);
+            const uint32_t m = (j & 1) ? m1 : m0;
+            mma16816(acc[j], a, vx[0][j >> 1] & m, vx[1][j >> 1] & m);
         }
     }
 }
@@ -243,7 +273,7 @@ attn_decode_kernel(const AttnParams p) {
     constexpr int LUTN = D + 1;
     constexpr int REC = kHeads * D + 8;  // 8*D sums, then the 8 weight totals
     __shared__ __align__(16) uint32_t kst_all[kWarps][32 * W];
-    __shared__ __align__(16) uint32_t vst_all[kWarps][32 * W];
+    __shared__ __align__(16) uint32_t vst_all[kWarps][2][32 * W];  // interleaved V pairs; [1] = shifted copy
     // weight tables indexed by bound - score: {hi, lo} fp16 pairs, then (kLutStride words on) the same
     // weights in fp32; an all-zero copy of both for dead keys and absent heads sits LUTN words further
     static_assert(2 * LUTN <= kLutStride, "table stride");
@@ -321,7 +351,8 @@ attn_decode_kernel(const AttnParams p) {
     const int end = min(len, begin + range);
 
     uint32_t* kst = kst_all[warp];
-    uint32_t* vst = vst_all[warp];
+    uint32_t* vst_w = vst_all[warp][0];                              // written at staging time
+    const uint32_t* vst = vst_all[warp][gid == 7 ? 1 : 0];           // read as the MMA operand
     const int first = begin + 32 * warp;  // this warp's first tile; the next one is kGranule keys on
 
     // Query words of this thread's head and their popcount (the softmax bound).
@@ -384,7 +415,18 @@ attn_decode_kernel(const AttnParams p) {
     for (int tile = first; tile < end; tile += kGranule) {
         // ---- stage the current tile (lane = key) and start the next one's loads --------------------
         store_row<W>(kst + lane * W, kn);
-        store_row<W>(vst + lane * W, vn);
+        {
+            // even lanes build the low half-words of their key pair, odd lanes the high ones
+            const uint32_t sel = (lane & 1) ? 0x3276u : 0x5410u;
+            uint32_t* dst = vst_w + (lane >> 1) * 2 * W + (lane & 1);
+#pragma unroll
+            for (int w = 0; w < W; ++w) {
+                const uint32_t other = __shfl_xor_sync(0xffffffffu, vn[w], 1);
+                const uint32_t x = prmt(vn[w], other, sel);
+                dst[2 * w] = x;
+                dst[32 * W + 2 * w] = (x >> 1) & 0x7fff7fffu;
+            }
+        }
         const unsigned live = __ballot_sync(0xffffffffu, ok_n);
         const int32_t phys_c = table_entry(tile + 2 * kGranule + lane);
         ok_n = fetch(tile + kGranule + lane, phys_b, kn, vn);
@@ -397,14 +439,18 @@ attn_decode_kernel(const AttnParams p) {
     }
 
     // ---- undo the scales; fold the warps; write the output row or one partial record --------------
-    // Column n of a channel block was multiplied by 2^(n - 24) (the V bit read as fp16); the lo rows by
+    // A column of a channel block was multiplied by the power of two its V bit reads as (VBits); the lo rows by
     // 2^11.  Sums and totals both keep the common factor 2^kScaleLog2.
-    const float u0 = __uint_as_float(static_cast<uint32_t>(127 + 24 - 2 * tig) << 23);
-    const float u1 = __uint_as_float(static_cast<uint32_t>(127 + 23 - 2 * tig) << 23);
+    float un[2][2];  // [byte parity][column 2tig, 2tig + 1]: 2^-log2_value
+#pragma unroll
+    for (int e = 0; e < 2; ++e)
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+            un[e][i] = __uint_as_float(static_cast<uint32_t>(127 - VBits::log2_value(2 * tig + i, e)) << 23);
 #pragma unroll
     for (int j = 0; j < 4 * W; ++j) {
-        const float v0 = (acc[j][0] + acc[j][2] * kLoUnscale) * u0;
-        const float v1 = (acc[j][1] + acc[j][3] * kLoUnscale) * u1;
+        const float v0 = (acc[j][0] + acc[j][2] * kLoUnscale) * un[j & 1][0];
+        const float v1 = (acc[j][1] + acc[j][3] * kLoUnscale) * un[j & 1][1];
         *reinterpret_cast<float2*>(&red[warp][gid * RS + 8 * j + 2 * tig]) = make_float2(v0, v1);
     }
     lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);  // the four threads of a head hold disjoint keys
@@ -487,7 +533,9 @@ int launch_attn_nw(const AttnParams& p, bool vec, cudaStream_t stream) {
 
 template <int W>
 int launch_attn(const AttnParams& p, bool vec, cudaStream_t stream) {
-    return p.granule == 256 ? launch_attn_nw<W, 8>(p, vec, stream) : launch_attn_nw<W, 4>(p, vec, stream);
+    if (W <= 3 && p.granule == 256) return launch_attn_nw<W, (W <= 3 ? 8 : 4)>(p, vec, stream);
+    if (p.granule != 128) return SPK_ERR_UNSUPPORTED;
+    return launch_attn_nw<W, 4>(p, vec, stream);
 }
 
 static inline int log2_exact(int x) {
