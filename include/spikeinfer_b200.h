@@ -193,12 +193,17 @@ int spk_add_rmsnorm(void* h, const void* delta, const void* weight, float eps, v
  * out      [T, n_seqs, H_q, head_dim] in out_dtype (F32/BF16/F16), strides so_t, so_n,
  *          so_h (channel stride 1) -- may be a view of a larger buffer.
  *
- * scores are exact integers popc(q & k); softmax and p.v accumulate in fp32.
- * K and V are read once per KV head, shared by the H_q/H_kv query heads of the group.
- * Long rows are split into key ranges whose partial sums live in `workspace`
- * (size from spk_attn_decode_workspace_bytes with the same arguments; may be NULL
- * when that returns 0).  head_dim must be a multiple of 32, <= 128; block_size a
- * power of two, >= 1.
+ * scores are exact integers popc(q & k); the softmax weights are carried as pairs of
+ * fp16 numbers (22 significant bits) and the weighted sum p.v runs on the tensor cores
+ * with fp32 accumulation (within 1e-6 of a float64 evaluation, relative to the largest
+ * output).  K and V are read once per KV head, shared by the H_q/H_kv query heads of
+ * the group.  When the batch alone cannot fill the GPU, rows are split into key ranges
+ * whose partial sums live in `workspace` (size from spk_attn_decode_workspace_bytes with
+ * the same arguments; may be NULL when that returns 0).  head_dim must be a multiple of
+ * 32, <= 128; block_size a power of two, >= 1; 0 <= scale and scale * head_dim <= 24
+ * (head_dim^-0.5, the reference's scale, always is), else SPK_ERR_UNSUPPORTED;
+ * max_blocks * block_size, num_blocks and the block/slot strides must fit 31 bits, else
+ * SPK_ERR_TOO_LARGE.
  * ------------------------------------------------------------------------- */
 int64_t spk_attn_decode_workspace_bytes(int T, int64_t n_seqs, int num_q_heads, int num_kv_heads,
                                         int head_dim, int block_size, int64_t max_blocks);
