@@ -38,6 +38,8 @@ class SpikeDecodeEngine:
         self.free_rows = list(range(max_num_seqs - 1, -1, -1))
         self.host_in = torch.zeros(max_num_seqs, dtype=torch.int64).pin_memory()
         self.host_out = torch.zeros(max_num_seqs, dtype=torch.int64).pin_memory()
+        self.token_log: torch.Tensor | None = None  # device log of decode_steps
+        self.host_log: torch.Tensor | None = None
 
     # -- prefill ----------------------------------------------------------
     @torch.no_grad()
@@ -120,6 +122,25 @@ class SpikeDecodeEngine:
             self.graph.replay()
         else:
             self._body()
+
+    @torch.no_grad()
+    def decode_steps(self, k: int) -> torch.Tensor:
+        """``k`` decode steps per host visit: the steps are enqueued back to back (each feeds the next from
+        ``state.next_tokens`` on the device), every step's tokens are kept in a device log, and the host
+        waits once, for a single ``[k, max_num_seqs]`` copy.  The reference visits the host after every
+        step (``sampler.py:81`` ``.tolist()``, ``llm_engine.py:359-387``); stop conditions are then checked on
+        the returned block, so up to ``k - 1`` tokens per finished row are decoded in vain."""
+        if k < 1:
+            raise ValueError("k must be at least 1")
+        if self.token_log is None or self.token_log.shape[0] < k:
+            self.token_log = torch.zeros(k, self.state.next_tokens.numel(), dtype=torch.int64, device=self.device)
+            self.host_log = torch.zeros(k, self.state.next_tokens.numel(), dtype=torch.int64).pin_memory()
+        for i in range(k):
+            self.decode_step()
+            self.token_log[i].copy_(self.state.next_tokens, non_blocking=True)
+        self.host_log[:k].copy_(self.token_log[:k], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return self.host_log[:k]
 
     @torch.no_grad()
     def step_host(self, tokens_in: torch.Tensor | None = None) -> torch.Tensor:

@@ -140,3 +140,21 @@ def test_host_in_the_loop_step(dev, golden):
         got.append(out.tolist())
         host.copy_(out)
     assert [list(t) for t in zip(*got)] == [t[1:5] for t in g["random_lif"]["tokens"]]
+
+
+def test_k_steps_per_host_visit(dev, golden):
+    """decode_steps(k): k graph replays enqueued back to back, one device-to-host copy; the block of tokens
+    equals the reference's tokens 1..k and the state afterwards continues the same sequence."""
+    g, shape, w = build(golden, "random_lif")
+    model = SpikingQwenModel(SpikingQwenConfig(**g["config"]), w, device=dev)
+    eng = SpikeDecodeEngine(model, g["num_blocks"], g["block_size"], max_num_seqs=4, max_model_len=g["max_len"])
+    eng.add_requests(tiny_prompts(shape.vocab_size))
+    want = g["random_lif"]["tokens"]
+    block = eng.decode_steps(6)
+    assert block.shape == (6, 4)
+    assert [list(t) for t in zip(*block.tolist())] == [t[1:7] for t in want]
+    block = eng.decode_steps(3)  # shorter block reuses the log
+    assert [list(t) for t in zip(*block.tolist())] == [t[7:10] for t in want]
+    eng.state.check_status()
+    with pytest.raises(ValueError):
+        eng.decode_steps(0)
