@@ -36,6 +36,11 @@ class AttentionMetadata:
     prefill_block_tables: list[torch.Tensor] = field(default_factory=list)
     status: torch.Tensor | None = None
     """Optional int32 ``[1]`` device word the kernels OR anomaly bits into."""
+    prefill_row_tables: torch.Tensor | None = None
+    """Optional int32 ``[n_prefill_tok, max_blocks]`` (see :func:`build_prefill_rows`): with it the prefill
+    chunks run through the packed popcount kernel in one batched launch instead of per-sequence SDPA."""
+    prefill_row_lens: torch.Tensor | None = None
+    """int32 ``[n_prefill_tok]``: keys visible to each prefill token (context + position in chunk + 1)."""
 
     @property
     def num_prefills(self) -> int:
@@ -51,7 +56,39 @@ class AttentionMetadata:
             num_decode_tokens=self.num_decode_tokens, block_tables=mv(self.block_tables),
             seq_lens=mv(self.seq_lens), prefill_query_starts=self.prefill_query_starts,
             prefill_query_lens=self.prefill_query_lens, prefill_context_lens=self.prefill_context_lens,
-            prefill_block_tables=[mv(t) for t in self.prefill_block_tables], status=mv(self.status))
+            prefill_block_tables=[mv(t) for t in self.prefill_block_tables], status=mv(self.status),
+            prefill_row_tables=mv(self.prefill_row_tables), prefill_row_lens=mv(self.prefill_row_lens))
+
+
+def build_prefill_rows(meta: AttentionMetadata, pad_block: int = 0) -> AttentionMetadata:
+    """Batched varlen prefill over the packed pool: every prefill token becomes one row of the decode kernel.
+
+    Token ``i`` of a chunk with ``c`` cached tokens sees keys ``0 .. c + i`` of its sequence, i.e. it is a
+    decode row of length ``c + i + 1`` over the sequence's block table; causal masking is the row length.
+    The chunk's own K/V are written before attention runs, as for decode rows.  Fills ``prefill_row_tables``
+    (each sequence's table repeated for its tokens, padded with ``pad_block``) and ``prefill_row_lens``; the
+    prefill chunks must be contiguous and in order behind the decode tokens.  The reference runs one SDPA per
+    sequence on unpacked spikes instead (``attention.py:161-178``)."""
+    if not meta.num_prefills:
+        return meta
+    device = meta.slot_mapping.device
+    width = max(int(t.numel()) for t in meta.prefill_block_tables)
+    tables, lens = [], []
+    expect = meta.num_decode_tokens
+    for start, q_len, ctx, table in zip(meta.prefill_query_starts, meta.prefill_query_lens,
+                                        meta.prefill_context_lens, meta.prefill_block_tables):
+        if start != expect:
+            raise ValueError("prefill chunks must be contiguous and ordered behind the decode tokens")
+        expect = start + q_len
+        if -(-(ctx + q_len) // meta.block_size) > table.numel():
+            raise ValueError("block table shorter than the chunk's context")
+        row = torch.full((width,), pad_block, dtype=torch.int32, device=device)
+        row[: table.numel()] = table.to(device=device, dtype=torch.int32)
+        tables.append(row.unsqueeze(0).expand(q_len, width))
+        lens.append(torch.arange(ctx + 1, ctx + q_len + 1, dtype=torch.int32, device=device))
+    meta.prefill_row_tables = torch.cat(tables).contiguous()
+    meta.prefill_row_lens = torch.cat(lens)
+    return meta
 
 
 def _causal_offset_mask(query_len: int, total_len: int, device, dtype) -> torch.Tensor:
@@ -100,7 +137,14 @@ def paged_attention(q_spk, k_spk, v_spk, k_cache, v_cache, meta: AttentionMetada
         paged_spike_attn_decode(pack_spikes(q_dec), k_cache, v_cache, meta.block_tables, meta.seq_lens,
                                 head_dim=head_dim, block_size=meta.block_size, num_q_heads=num_q_heads,
                                 num_kv_heads=num_kv_heads, out=out[:, :n_dec], status=meta.status)
-    _prefill_chunks(q_spk[:, 0], k_cache, v_cache, meta, out, num_q_heads, num_kv_heads, head_dim)
+    if meta.num_prefills and meta.prefill_row_tables is not None:
+        n_pre = meta.prefill_row_lens.numel()
+        q_pre = q_spk[:, 0, :, n_dec:n_dec + n_pre, :].permute(0, 2, 1, 3)
+        paged_spike_attn_decode(pack_spikes(q_pre), k_cache, v_cache, meta.prefill_row_tables, meta.prefill_row_lens,
+                                head_dim=head_dim, block_size=meta.block_size, num_q_heads=num_q_heads,
+                                num_kv_heads=num_kv_heads, out=out[:, n_dec:n_dec + n_pre], status=meta.status)
+    else:
+        _prefill_chunks(q_spk[:, 0], k_cache, v_cache, meta, out, num_q_heads, num_kv_heads, head_dim)
     return out.view(T, 1, n_tok, num_q_heads * head_dim)
 
 
@@ -125,7 +169,8 @@ def fused_qkv_attention(qkv: torch.Tensor, lif_q, lif_k, lif_v, k_cache, v_cache
     xv = qkv[..., (hq + hkv) * d:].unflatten(-1, (hkv, d))
     q_packed = torch.empty((T, n_tok, hq, W), dtype=torch.int32, device=device)
     q_dense = None
-    if meta.num_prefills:
+    packed_prefill = meta.num_prefills and meta.prefill_row_tables is not None
+    if meta.num_prefills and not packed_prefill:
         q_dense = torch.empty((T, hq, n_tok, d), dtype=dtype, device=device)
     kc, vc = _flat_pool(k_cache), _flat_pool(v_cache)
     num_slots = kc.shape[2]
@@ -147,6 +192,11 @@ def fused_qkv_attention(qkv: torch.Tensor, lif_q, lif_k, lif_v, k_cache, v_cache
         paged_spike_attn_decode(q_packed[:, :n_dec], k_cache, v_cache, meta.block_tables, meta.seq_lens,
                                 head_dim=d, block_size=meta.block_size, num_q_heads=hq, num_kv_heads=hkv,
                                 out=out[:, :n_dec], status=meta.status)
-    if meta.num_prefills:
+    if packed_prefill:
+        n_pre = meta.prefill_row_lens.numel()
+        paged_spike_attn_decode(q_packed[:, n_dec:n_dec + n_pre], k_cache, v_cache, meta.prefill_row_tables,
+                                meta.prefill_row_lens, head_dim=d, block_size=meta.block_size, num_q_heads=hq,
+                                num_kv_heads=hkv, out=out[:, n_dec:n_dec + n_pre], status=meta.status)
+    elif meta.num_prefills:
         _prefill_chunks(q_dense, k_cache, v_cache, meta, out, hq, hkv, d)
     return out.view(T, n_tok, hq * d)

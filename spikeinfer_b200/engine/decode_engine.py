@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import torch
 
-from ..attention import AttentionMetadata
+from ..attention import AttentionMetadata, build_prefill_rows
 from ..modeling import SpikingQwenModel
 from .batch_state import DecodeBatchState
 from .spike_cache import PagedSpikeCache
@@ -20,7 +20,7 @@ from .spike_cache import PagedSpikeCache
 
 class SpikeDecodeEngine:
     def __init__(self, model: SpikingQwenModel, num_blocks: int, block_size: int = 16, max_num_seqs: int = 64,
-                 max_model_len: int = 4096, use_graph: bool = True) -> None:
+                 max_model_len: int = 4096, use_graph: bool = True, packed_prefill: bool = True) -> None:
         c = model.config
         self.model = model
         self.device = model.device
@@ -34,6 +34,9 @@ class SpikeDecodeEngine:
             slot_mapping=self.state.slot_mapping, block_size=block_size, num_decode_tokens=max_num_seqs,
             block_tables=self.state.block_tables, seq_lens=self.state.seq_lens, status=self.state.status)
         self.use_graph = use_graph
+        # prompts attend through the packed popcount kernel in one batched launch per layer (False: one SDPA
+        # per sequence on unpacked spikes, as the reference does)
+        self.packed_prefill = packed_prefill
         self.graph: torch.cuda.CUDAGraph | None = None
         self.free_rows = list(range(max_num_seqs - 1, -1, -1))
         self.host_in = torch.zeros(max_num_seqs, dtype=torch.int64).pin_memory()
@@ -63,6 +66,8 @@ class SpikeDecodeEngine:
             slot_mapping=torch.cat(slot_parts), block_size=bs, prefill_query_starts=starts,
             prefill_query_lens=lens, prefill_context_lens=[0] * len(lens), prefill_block_tables=tables,
             status=self.state.status)
+        if self.packed_prefill:
+            build_prefill_rows(meta, pad_block=self.cache.pad_block)
         input_ids = torch.tensor(ids, dtype=torch.int64, device=dev)
         hidden = self.model.forward_paged(input_ids, torch.cat(pos), self.cache.layers, meta)
         last = torch.tensor([s + n - 1 for s, n in zip(starts, lens)], dtype=torch.int64, device=dev)

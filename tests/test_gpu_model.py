@@ -91,9 +91,10 @@ def test_per_layer_operators_bit_exact_on_oracle_tensors(variant, dev, golden):
             assert torch.equal(prod.cpu(), c["gate_spk"] * up + 0.0), f"{step} layer {i}: gated product differs"
 
 
+@pytest.mark.parametrize("packed_prefill", [True, False])
 @pytest.mark.parametrize("use_graph", [False, True])
 @pytest.mark.parametrize("variant", ["constant_lif", "random_lif"])
-def test_engine_tokens_match_reference(variant, use_graph, dev, golden):
+def test_engine_tokens_match_reference(variant, use_graph, packed_prefill, dev, golden):
     """4 prompts x 32 tokens, 16 greedy tokens: the engine (eager and CUDA-graph decode, device-built
     metadata) reproduces the reference's tokens; pools match the oracle's wherever tokens matched."""
     g, shape, w = build(golden, variant)
@@ -101,7 +102,7 @@ def test_engine_tokens_match_reference(variant, use_graph, dev, golden):
     model = SpikingQwenModel(SpikingQwenConfig(**g["config"]), w, device=dev)
     assert model.validate_thresholds()
     eng = SpikeDecodeEngine(model, g["num_blocks"], g["block_size"], max_num_seqs=8, max_model_len=g["max_len"],
-                            use_graph=use_graph)
+                            use_graph=use_graph, packed_prefill=packed_prefill)
     rows = eng.add_requests(tiny_prompts(shape.vocab_size))
     assert rows == [0, 1, 2, 3]
     toks = [[int(eng.state.next_tokens[r])] for r in rows]
@@ -158,3 +159,51 @@ def test_k_steps_per_host_visit(dev, golden):
     eng.state.check_status()
     with pytest.raises(ValueError):
         eng.decode_steps(0)
+
+
+def test_packed_prefill_equals_sdpa_prefill_with_cached_context(dev):
+    """A mixed batch (2 decode rows, then two prefill chunks, one of them continuing a cached prefix) through
+    fused_qkv_attention: the batched popcount prefill and the per-sequence SDPA prefill agree to 1e-5, and the
+    decode rows are untouched by the choice."""
+    from spikeinfer_b200.attention import build_prefill_rows, fused_qkv_attention
+    torch.manual_seed(11)
+    T, hq, hkv, d, bs = 4, 4, 2, 64, 16
+    num_blocks = 40
+    k_cache = torch.zeros(T, hkv, num_blocks * bs, 2, dtype=torch.int32, device=dev)
+    v_cache = torch.zeros_like(k_cache)
+    # cached state: decode rows of 20 and 37 tokens, a prefix of 19 tokens for the second chunk
+    g = torch.Generator().manual_seed(3)
+    filled = (torch.rand(T, hkv, num_blocks * bs, 64, generator=g) < 0.3)
+    from oracle import torch_oracle
+    k_cache.copy_(torch_oracle.pack_spikes(filled.float()).to(dev))
+    v_cache.copy_(torch_oracle.pack_spikes((torch.rand(T, hkv, num_blocks * bs, 64, generator=g) < 0.3).float()).to(dev))
+    tables = {"d0": [3, 9], "d1": [1, 17, 30], "p0": [5, 6, 7], "p1": [20, 2, 11, 12]}
+    dec_lens = [20, 37]
+    chunks = [(0, 40), (19, 33)]  # (cached context, new tokens)
+    slots = [tables["d0"][(20 - 1) // bs] * bs + (20 - 1) % bs, tables["d1"][(37 - 1) // bs] * bs + (37 - 1) % bs]
+    for name, (ctx, n) in zip(("p0", "p1"), chunks):
+        slots += [tables[name][p // bs] * bs + p % bs for p in range(ctx, ctx + n)]
+    n_tok = 2 + 40 + 33
+    bt = torch.full((2, 4), num_blocks - 1, dtype=torch.int32)
+    bt[0, :2] = torch.tensor(tables["d0"]); bt[1, :3] = torch.tensor(tables["d1"])
+    def meta():
+        return AttentionMetadata(
+            slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev), block_size=bs, num_decode_tokens=2,
+            block_tables=bt.to(dev), seq_lens=torch.tensor(dec_lens, dtype=torch.int32, device=dev),
+            prefill_query_starts=[2, 42], prefill_query_lens=[40, 33], prefill_context_lens=[0, 19],
+            prefill_block_tables=[torch.tensor(tables["p0"], dtype=torch.int32, device=dev),
+                                  torch.tensor(tables["p1"], dtype=torch.int32, device=dev)])
+    qkv = torch.randn(T, n_tok, (hq + 2 * hkv) * d, device=dev)
+    lif = lambda n: (torch.full((n,), 0.9, device=dev), torch.full((n,), 0.8, device=dev))
+    outs = []
+    for packed in (False, True):
+        kc, vc = k_cache.clone(), v_cache.clone()
+        m = meta()
+        if packed:
+            build_prefill_rows(m, pad_block=num_blocks - 1)
+            assert m.prefill_row_tables.shape == (73, 4) and m.prefill_row_lens.tolist() == list(range(1, 41)) + list(range(20, 53))
+        outs.append(fused_qkv_attention(qkv, lif(d), lif(d), lif(d), kc, vc, m, hq, hkv, d))
+    sdpa, packed = outs
+    assert torch.equal(sdpa[:, :2], packed[:, :2])
+    err = ((sdpa - packed).abs().max() / sdpa.abs().max()).item()
+    assert err < 1e-5, f"{err:.2e}"

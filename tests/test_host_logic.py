@@ -76,3 +76,30 @@ def test_validate_thresholds():
     bad = torch.nn.Sequential(Site([0.5, 1.0]), Site([0.0, 0.2]))
     with pytest.raises(ValueError, match="threshold > 0"):
         kernels.validate_thresholds(bad)
+
+
+def test_build_prefill_rows_turns_chunks_into_decode_rows():
+    """Every prefill token becomes a decode row of length context + index + 1 over its sequence's table."""
+    from spikeinfer_b200.attention import AttentionMetadata, build_prefill_rows
+    meta = AttentionMetadata(
+        slot_mapping=torch.zeros(1 + 3 + 2, dtype=torch.int64), block_size=4, num_decode_tokens=1,
+        prefill_query_starts=[1, 4], prefill_query_lens=[3, 2], prefill_context_lens=[0, 5],
+        prefill_block_tables=[torch.tensor([7], dtype=torch.int32), torch.tensor([2, 9], dtype=torch.int32)])
+    build_prefill_rows(meta, pad_block=31)
+    assert meta.prefill_row_lens.tolist() == [1, 2, 3, 6, 7]
+    assert meta.prefill_row_tables.tolist() == [[7, 31]] * 3 + [[2, 9]] * 2
+    assert meta.prefill_row_tables.dtype == torch.int32 and meta.prefill_row_tables.is_contiguous()
+    # chunks out of place, or a table too short for the context, are refused
+    bad = AttentionMetadata(slot_mapping=torch.zeros(3, dtype=torch.int64), block_size=4, num_decode_tokens=0,
+                            prefill_query_starts=[1], prefill_query_lens=[2], prefill_context_lens=[0],
+                            prefill_block_tables=[torch.tensor([0], dtype=torch.int32)])
+    with pytest.raises(ValueError):
+        build_prefill_rows(bad)
+    short = AttentionMetadata(slot_mapping=torch.zeros(2, dtype=torch.int64), block_size=4, num_decode_tokens=0,
+                              prefill_query_starts=[0], prefill_query_lens=[2], prefill_context_lens=[7],
+                              prefill_block_tables=[torch.tensor([0, 1], dtype=torch.int32)])
+    with pytest.raises(ValueError):
+        build_prefill_rows(short)
+    # no prefill chunks: nothing to do
+    none = AttentionMetadata(slot_mapping=torch.zeros(1, dtype=torch.int64), block_size=4, num_decode_tokens=1)
+    assert build_prefill_rows(none).prefill_row_tables is None
