@@ -65,6 +65,22 @@ struct Lif {
     }
 };
 
+// ORs the bytes of the four lanes that build one packed word (lane & 3 = byte position) into every one of
+// them.  A shuffle under a mask that differs between lanes is expanded by the compiler into a match/vote loop
+// over the distinct masks (measured: ~7 of 17.8 instructions per element of the fused kernel), so a warp whose
+// lanes are all live -- every warp but the edge ones -- shuffles under the full mask; `all_live` must be
+// warp-uniform.  Otherwise only the group's own lanes take part (dead groups have left the loop body).
+__device__ __forceinline__ uint32_t gather_word(uint32_t word, bool all_live, unsigned group_mask) {
+    if (all_live) {
+        word |= __shfl_xor_sync(0xffffffffu, word, 1);
+        word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    } else {
+        word |= __shfl_xor_sync(group_mask, word, 1);
+        word |= __shfl_xor_sync(group_mask, word, 2);
+    }
+    return word;
+}
+
 __device__ __forceinline__ void store_bit(void* base, int dtype, int64_t idx, bool b) {
     switch (dtype) {
         case SPK_F32: static_cast<float*>(base)[idx] = spk_bit_as<float>(b); break;
@@ -336,8 +352,10 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
             cp_async_wait<kStages - 1>();  // this lane's copies for token j have landed
         }
         // The four lanes of a word share (token group, head, word), so they are live or dead together and a
-        // dead group can skip the token entirely (the shuffles below only involve its own four lanes).
-        if (!(in_range && tok < n_tok)) continue;
+        // dead group skips the token; the byte exchange (gather_word) then runs under the group's own mask.
+        const bool live = in_range && tok < n_tok;
+        const bool all_live = __all_sync(0xffffffffu, live);
+        if (!live) continue;
         const int64_t row = tok * s.H + h;
         Lif st[kSeg];
         {
@@ -399,8 +417,7 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
                     if (has_dense) store_dense8(s.dense, s.dense_dtype, dense_idx + i * sd_t, bits);
                 }
                 uint32_t word = bits << (8 * sub);
-                word |= __shfl_xor_sync(group_mask, word, 1);
-                word |= __shfl_xor_sync(group_mask, word, 2);
+                word = gather_word(word, all_live, group_mask);
                 if (sub == i) mine = word;
             }
             if (wp != nullptr && (FULL || sub < T)) *wp = mine;
@@ -444,8 +461,7 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
                     if (has_dense) store_dense8(s.dense, s.dense_dtype, dense_idx + (t0 + i) * sd_t, bits);
                 }
                 uint32_t word = bits << (8 * sub);
-                word |= __shfl_xor_sync(group_mask, word, 1);
-                word |= __shfl_xor_sync(group_mask, word, 2);
+                word = gather_word(word, all_live, group_mask);
                 if (sub == i) mine = word;
             }
             if (wp != nullptr && (FULL || t0 + sub < T)) *wp = mine;
