@@ -7,6 +7,8 @@
 // on its own (no FMA contraction: the __f*_rn intrinsics are never fused); the
 // reset r is taken from the previous membrane; a spike is (u - theta) > 0 (see the
 // note at struct Lif on why comparing u > theta directly is the same predicate here).
+#include <utility>
+
 #include "spk_common.cuh"
 
 namespace {
@@ -55,6 +57,30 @@ struct Lif {
                 "@p or.b32 %1, %1, %5;\n\t}"
                 : "+f"(u), "+r"(bits)
                 : "f"(beta), "f"(cur), "f"(th), "r"(bit));
+        }
+    }
+    // Same step with the spike's bit as an immediate operand (no register holds the constant).
+    template <int MODE, uint32_t BIT>
+    __device__ __forceinline__ void step_bit(float cur, float beta, float th, uint32_t& bits) {
+        if (MODE == SPK_RESET_SUBTRACT_DELAYED) {
+            asm("{\n\t.reg .pred p;\n\t"
+                "mul.rn.f32 %0, %3, %0;\n\t"
+                "add.rn.f32 %0, %0, %4;\n\t"
+                "sub.rn.f32 %0, %0, %1;\n\t"
+                "setp.gt.f32 p, %0, %5;\n\t"
+                "selp.f32 %1, %5, 0f00000000, p;\n\t"
+                "@p or.b32 %2, %2, %6;\n\t}"
+                : "+f"(u), "+f"(rth), "+r"(bits)
+                : "f"(beta), "f"(cur), "f"(th), "n"(BIT));
+        } else {
+            asm("{\n\t.reg .pred p;\n\t"
+                "mul.rn.f32 %0, %2, %0;\n\t"
+                "add.rn.f32 %0, %0, %3;\n\t"
+                "setp.gt.f32 p, %0, %4;\n\t"
+                "@p mov.f32 %0, 0f00000000;\n\t"
+                "@p or.b32 %1, %1, %5;\n\t}"
+                : "+f"(u), "+r"(bits)
+                : "f"(beta), "f"(cur), "f"(th), "n"(BIT));
         }
     }
     template <int MODE>
@@ -191,6 +217,13 @@ struct Raw8<__half> {
 };
 
 
+// One timestep of the 8 channels of a segment; bit c of `bits` = spike of channel c.
+template <int MODE, typename TX, int... C>
+__device__ __forceinline__ void step8(Lif (&st)[8], const Raw8<TX>& raw, const float (&b)[8], const float (&th)[8],
+                                      uint32_t& bits, std::integer_sequence<int, C...>) {
+    (st[C].template step_bit<MODE, (1u << C)>(raw.get(C), b[C], th[C], bits), ...);
+}
+
 // Rounds an fp32 value to the element type TX and back (what a torch elementwise op in that dtype does).
 template <typename TX>
 __device__ __forceinline__ float round_to(float v);
@@ -274,7 +307,9 @@ constexpr int kStages = 3;  // tokens in flight per lane in the streaming form
 // currents (and multiplicands) of the next kStages-1 tokens in flight with cp.async into its own slots
 // of shared memory, so the bytes in flight per SM no longer depend on how many registers a warp holds.
 // Every lane reads back only what it copied itself, so no barrier is involved.  Needs T <= 4, no RoPE.
-template <typename TX, int MODE, bool ROPE, bool FULL, bool ASYNC>
+// PLAIN: the site has no initial membrane, dense output, gated product or rotary embedding (checked on the
+// host); the feature tests below then fold away at compile time.
+template <typename TX, int MODE, bool ROPE, bool FULL, bool ASYNC, bool PLAIN>
 __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t units, uint32_t per_tok,
                                                uint32_t per_row, int toks, uint32_t unit, int lane, int T,
                                                int64_t n_tok, uint32_t* status, uint4* stage, int slots) {
@@ -303,14 +338,15 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
     }
     const int sub = lane & 3;  // position of this lane's byte within its word
     // rotary embedding: channel c pairs with c + N/2 (first half, negated partner) or c - N/2 (second half)
-    const bool rope = ROPE && s.rope_cos != nullptr;
+    const bool rope = !PLAIN && ROPE && s.rope_cos != nullptr;
     const bool first_half = 2 * sg < per_row;
     const int64_t partner_off = first_half ? s.N / 2 : -(s.N / 2);
     const float partner_sign = first_half ? -1.0f : 1.0f;
 
     // Site fields used in the loops, read once.
     const int64_t sx_t = s.sx_t, so_t = s.so_t, sd_t = s.sd_t, sm_t = s.sm_t, sg_t = s.sg_t, N = s.N;
-    const bool has_packed = s.packed != nullptr, has_dense = s.dense != nullptr, has_gated = s.gated != nullptr;
+    const bool has_packed = s.packed != nullptr, has_dense = !PLAIN && s.dense != nullptr;
+    const bool has_gated = !PLAIN && s.gated != nullptr;
     const unsigned group_mask = 0xFu << (lane & 28);  // the four lanes that build one word together
 
     constexpr int VECS = sizeof(TX) * kSeg / 16;  // 16-byte pieces of one 8-channel segment
@@ -360,7 +396,7 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
         Lif st[kSeg];
         {
             float u0[kSeg] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (s.mem0 != nullptr) {
+            if (!PLAIN && s.mem0 != nullptr) {
                 const float4 m0 = __ldg(reinterpret_cast<const float4*>(s.mem0 + row * N + c0));
                 const float4 m1 = __ldg(reinterpret_cast<const float4*>(s.mem0 + row * N + c0) + 1);
                 u0[0] = m0.x; u0[1] = m0.y; u0[2] = m0.z; u0[3] = m0.w;
@@ -404,8 +440,7 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
                 if (FULL || i < T) {
                     Raw8<TX> raw;
                     raw.from_smem(mine_stage + i * VECS * 32);
-#pragma unroll
-                    for (int c = 0; c < kSeg; ++c) st[c].template step<MODE>(raw.get(c), b[c], th[c], 1u << c, bits);
+                    step8<MODE, TX>(st, raw, b, th, bits, std::make_integer_sequence<int, kSeg>{});
                     if (has_gated) {
                         Raw8<TX> m;
                         m.from_smem(mine_stage + (kStepGroup + i) * VECS * 32);
@@ -477,7 +512,7 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
     }
 }
 
-template <int MODE, bool ROPE, bool FULL, bool ASYNC>
+template <int MODE, bool ROPE, bool FULL, bool ASYNC, bool PLAIN>
 __global__ void __launch_bounds__(kFusedThreads, ROPE ? 1 : (ASYNC ? 4 : 2))
 lif_pack_scatter_vec_kernel(VecArgs args, int T, int64_t n_tok, uint32_t* status) {
     extern __shared__ uint4 stage_smem[];
@@ -489,7 +524,7 @@ lif_pack_scatter_vec_kernel(VecArgs args, int T, int64_t n_tok, uint32_t* status
     // this lane's slots: [warp][stage][slot][lane]
     uint4* stage = ASYNC ? stage_smem + (threadIdx.x >> 5) * kStages * args.slots * 32 + lane : nullptr;
 #define SPK_SITE(TX_) \
-    fused_site_vec<TX_, MODE, ROPE, FULL, ASYNC>(s, args.units[site], args.per_tok[site], args.per_row[site], \
+    fused_site_vec<TX_, MODE, ROPE, FULL, ASYNC, PLAIN>(s, args.units[site], args.per_tok[site], args.per_row[site], \
                                                  args.toks, unit, lane, T, n_tok, status, stage, args.slots)
     switch (s.x_dtype) {
         case SPK_F32: SPK_SITE(float); break;
@@ -767,9 +802,13 @@ extern "C" int spk_lif_pack_scatter(const spk_lif_site* sites, int n_sites, int 
             cudaStream_t vst = spk_stream(stream);
             const bool sub = reset_mode == SPK_RESET_SUBTRACT_DELAYED;
             const bool full = T % kStepGroup == 0;  // no partial group of timesteps: the per-step bounds checks drop out
-#define SPK_LAUNCH_VEC(MODE_, ROPE_, FULL_, ASYNC_)                                                                   \
+            bool plain = true;  // packed bits (+ final membrane) only: the feature tests fold away
+            for (int i = 0; i < n_sites; ++i)
+                plain = plain && sites[i].mem0 == nullptr && sites[i].dense == nullptr && sites[i].gated == nullptr &&
+                        sites[i].rope_cos == nullptr;
+#define SPK_LAUNCH_VEC(MODE_, ROPE_, FULL_, ASYNC_, PLAIN_)                                                                \
     do {                                                                                                              \
-        auto kern = lif_pack_scatter_vec_kernel<MODE_, ROPE_, FULL_, ASYNC_>;                                         \
+        auto kern = lif_pack_scatter_vec_kernel<MODE_, ROPE_, FULL_, ASYNC_, PLAIN_>;                                       \
         if (stage_bytes > 48 * 1024) {                                                                                \
             const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
                                                        static_cast<int>(stage_bytes));                                \
@@ -779,9 +818,10 @@ extern "C" int spk_lif_pack_scatter(const spk_lif_site* sites, int n_sites, int 
     } while (0)
 #define SPK_LAUNCH_MODE(MODE_)                                                          \
     do {                                                                                \
-        if (streaming) { if (full) SPK_LAUNCH_VEC(MODE_, false, true, true); else SPK_LAUNCH_VEC(MODE_, false, false, true); } \
-        else if (any_rope) { if (full) SPK_LAUNCH_VEC(MODE_, true, true, false); else SPK_LAUNCH_VEC(MODE_, true, false, false); } \
-        else { if (full) SPK_LAUNCH_VEC(MODE_, false, true, false); else SPK_LAUNCH_VEC(MODE_, false, false, false); } \
+        if (streaming && full && plain) SPK_LAUNCH_VEC(MODE_, false, true, true, true); \
+        else if (streaming) { if (full) SPK_LAUNCH_VEC(MODE_, false, true, true, false); else SPK_LAUNCH_VEC(MODE_, false, false, true, false); } \
+        else if (any_rope) { if (full) SPK_LAUNCH_VEC(MODE_, true, true, false, false); else SPK_LAUNCH_VEC(MODE_, true, false, false, false); } \
+        else { if (full) SPK_LAUNCH_VEC(MODE_, false, true, false, false); else SPK_LAUNCH_VEC(MODE_, false, false, false, false); } \
     } while (0)
             if (sub) SPK_LAUNCH_MODE(SPK_RESET_SUBTRACT_DELAYED);
             else SPK_LAUNCH_MODE(SPK_RESET_HARD_ZERO);
