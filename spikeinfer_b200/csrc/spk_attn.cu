@@ -59,6 +59,7 @@ struct AttnParams {
     int bs_log2; int max_keys, num_blocks;  // max_keys = max_blocks * block_size, below 2^31 (host-checked)
     float scale;
     float* ws; int splits; int granule;  // granule: keys per CTA step = 32 x warps per CTA
+    int longest_first;  // rank rows by length in-kernel (only worth its dependent load when CTAs outnumber the slots)
     uint32_t* status;
     int64_t items;
 };
@@ -295,7 +296,7 @@ attn_decode_kernel(const AttnParams p) {
     const int gp = static_cast<int>(rest % (p.Hkv * p.passes)); rest /= (p.Hkv * p.passes);
     const int c = static_cast<int>(rest % p.splits); rest /= p.splits;
     int64_t n = rest;
-    if (p.n_seqs <= 128 && p.n_seqs > 1) {
+    if (p.longest_first) {
         // Longest rows first (coarsely): rows are ranked by length class (8 classes of max_keys / 8 keys),
         // ties by index, and this item serves the row of rank `rest`.  The long-running CTAs are thus
         // scheduled early and the last wave holds short rows.  Ballots over the lengths held one or a
@@ -673,6 +674,9 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
     p.scale = scale; p.ws = static_cast<float*>(workspace); p.splits = pl.splits; p.granule = 32 * pl.warps;
     p.status = status;
     p.items = n_seqs * T * num_kv_heads * pl.passes * pl.splits;
+    // all CTAs resident at once: their order does not matter, and skipping the ranking takes one dependent
+    // global load off the start of every CTA
+    p.longest_first = n_seqs > 1 && n_seqs <= 128 && p.items > 148LL * (kSmWarps / pl.warps);
 
     const int W = head_dim / 32;
     const bool vec = aligned_to(k, sk_t, sk_h, sk_blk, sk_slot, W) && aligned_to(v, sv_t, sv_h, sv_blk, sv_slot, W);
