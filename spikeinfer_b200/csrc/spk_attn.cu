@@ -22,9 +22,11 @@
 //        left is either 0 or the fp16 subnormal 2^(i-24) for bit i.  Products with it are exact, and
 //        the known power of two is removed from the accumulators once, after the last key;
 //    The softmax denominators are plain fp32 sums of the same weights (a second table lookup per key).
-//    One 32-key tile of a 64-channel head costs 16 MMAs and about 250 instructions per warp, against
-//    about 620 instructions for the same tile as fp32 bit-selected adds on the SIMT pipes.  The
-//    register-fragment MMA path is the limit now (its pipe is busy ~80 % of the active cycles).
+//    One 32-key tile of a 64-channel head costs 16 MMAs and about 220 instructions per warp, against
+//    about 620 instructions for the same tile as fp32 bit-selected adds on the SIMT pipes.  No single
+//    unit is the limit (halving the MMAs as a timing probe, dropping a third of the integer operations,
+//    a quarter of the shared-memory traffic or doubling the resident warps each moved the time by
+//    -3 % .. +20 %); the kernel is bound by dependency latency within a warp's tile.
 #include "spk_common.cuh"
 
 namespace {
