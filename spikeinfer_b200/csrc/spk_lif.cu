@@ -470,18 +470,29 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
                     if (on) partner[i].load(xp + i * sx_t + partner_off);
                 }
             }
+            // The loads above are all in flight at once; the arithmetic below is a ROLLED loop over the group's
+            // timesteps (the step's registers are picked by a switch).  A small launch runs this code once per
+            // thread, so its duration is the time to fetch the instructions: unrolled, the q/k/v launch of a
+            // decode step spent 7.7 stall cycles per issued instruction waiting for instructions (ncu).
             uint32_t mine = 0;
-#pragma unroll
+#pragma unroll 1
             for (int i = 0; i < kStepGroup; ++i) {
                 uint32_t bits = 0;
                 if (FULL || t0 + i < T) {
+                    Raw8<TX> x_i, partner_i, mul_i;
+                    switch (i) {
+                        case 0: x_i = raw[0]; partner_i = partner[0]; mul_i = mulv[0]; break;
+                        case 1: x_i = raw[1]; partner_i = partner[1]; mul_i = mulv[1]; break;
+                        case 2: x_i = raw[2]; partner_i = partner[2]; mul_i = mulv[2]; break;
+                        default: x_i = raw[3]; partner_i = partner[3]; mul_i = mulv[3]; break;
+                    }
 #pragma unroll
                     for (int c = 0; c < kSeg; ++c) {
-                        float cur = raw[i].get(c);
+                        float cur = x_i.get(c);
                         if (rope) {
                             // (x * cos) + (rotate_half(x) * sin), every operation rounded to the model dtype
                             const float a = round_to<TX>(__fmul_rn(cur, rc[c]));
-                            const float r = round_to<TX>(__fmul_rn(partner_sign * partner[i].get(c), rs[c]));
+                            const float r = round_to<TX>(__fmul_rn(partner_sign * partner_i.get(c), rs[c]));
                             cur = round_to<TX>(__fadd_rn(a, r));
                         }
                         st[c].template step<MODE>(cur, b[c], th[c], 1u << c, bits);
@@ -490,7 +501,7 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
                         // gated[t, tok, h, c] = spike ? mul[t, tok, h, c] : 0   (the spike * up product)
                         float g[kSeg];
 #pragma unroll
-                        for (int c = 0; c < kSeg; ++c) g[c] = (bits >> c) & 1u ? mulv[i].get(c) : 0.0f;
+                        for (int c = 0; c < kSeg; ++c) g[c] = (bits >> c) & 1u ? mul_i.get(c) : 0.0f;
                         store8<TX>(gp + i * sg_t, g);
                     }
                     if (has_dense) store_dense8(s.dense, s.dense_dtype, dense_idx + (t0 + i) * sd_t, bits);
