@@ -180,6 +180,17 @@ int spk_add_rmsnorm(void* h, const void* delta, const void* weight, float eps, v
                     int64_t hidden, int dtype, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * Greedy sampling: out[r] = argmax over x[r, 0..cols) with torch.argmax's rules (first index of the
+ * largest value; NaN is larger than everything).  Replaces `logits.argmax(dim=-1)` of the sampler
+ * (spikeinfer/engine/sampler.py:63-81) so that the choice stays on the device, inside the captured
+ * decode step.  x [rows, cols] in F32/BF16/F16 with row stride row_stride (elements); out int64 [rows];
+ * workspace of spk_argmax_workspace_bytes(rows) bytes, 8-byte aligned.  rows <= 65535.
+ * ------------------------------------------------------------------------- */
+int64_t spk_argmax_workspace_bytes(int64_t rows);
+int spk_argmax(const void* x, int dtype, int64_t rows, int64_t cols, int64_t row_stride, int64_t* out,
+               void* workspace, int64_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Paged popcount decode attention.  Replaces paged_spike_attn_decode /
  * _paged_spike_attn_decode_kernel (spikeinfer/kernels/spike_attention.py:153-221,
  * :67-150) and the SWAR _popc (:52-65).

@@ -92,6 +92,8 @@ SIGNATURES = {
                         c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]),
     "spk_lif_pack_scatter": (c_int, [POINTER(LifSite), c_int, c_int, c_int64, c_int, c_void_p, c_void_p]),
     "spk_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int, c_void_p]),
+    "spk_argmax_workspace_bytes": (c_int64, [c_int64]),
+    "spk_argmax": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
     "spk_attn_decode_workspace_bytes": (c_int64, [c_int, c_int64, c_int, c_int, c_int, c_int, c_int64]),
     "spk_attn_decode": (c_int, [
         c_void_p, c_int64, c_int64, c_int64,

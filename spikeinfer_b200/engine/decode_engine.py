@@ -13,6 +13,7 @@ from __future__ import annotations
 import torch
 
 from ..attention import AttentionMetadata, build_prefill_rows
+from ..kernels import argmax_rows, argmax_workspace_bytes
 from ..modeling import SpikingQwenModel
 from .batch_state import DecodeBatchState
 from .spike_cache import PagedSpikeCache
@@ -43,6 +44,7 @@ class SpikeDecodeEngine:
         self.free_rows = list(range(max_num_seqs - 1, -1, -1))
         self.host_in = torch.zeros(max_num_seqs, dtype=torch.int64).pin_memory()
         self.host_out = torch.zeros(max_num_seqs, dtype=torch.int64).pin_memory()
+        self.sample_ws = torch.empty(argmax_workspace_bytes(max_num_seqs), dtype=torch.uint8, device=self.device)
         self.token_log: torch.Tensor | None = None  # device log of decode_steps
         self.host_log: torch.Tensor | None = None
 
@@ -94,7 +96,7 @@ class SpikeDecodeEngine:
         st.advance()
         hidden = self.model.forward_paged(st.input_ids, st.positions, self.cache.layers, self.meta)
         logits = self.model.compute_logits(hidden)
-        torch.argmax(logits, dim=-1, out=st.next_tokens)
+        argmax_rows(logits, out=st.next_tokens, workspace=self.sample_ws)  # greedy, inside the graph
 
     @torch.no_grad()
     def capture(self) -> None:

@@ -10,6 +10,7 @@ from .lif import (
     validate_thresholds,
 )
 from .norm import add_rms_norm
+from .sampling import argmax_rows, argmax_workspace_bytes
 from .packing import BITS_PER_WORD, pack_spikes, packed_bytes_per_token, packed_width, unpack_spikes
 from .spike_attention import (
     gather_kv_unpacked,
@@ -25,6 +26,8 @@ __all__ = [
     "lif_pack",
     "lif_gate_mul",
     "add_rms_norm",
+    "argmax_rows",
+    "argmax_workspace_bytes",
     "LifSiteSpec",
     "SUBTRACT_DELAYED",
     "HARD_ZERO",

@@ -71,3 +71,31 @@ def test_pool_exhaustion_and_full_table_are_flagged(dev):
     state2.advance()
     assert state2.status.item() & _lib.STATUS_TABLE_FULL
     assert state2.seq_lens[0].item() == 2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_argmax_rows_matches_torch(dtype, dev):
+    """Greedy sampling kernel against torch.argmax: ragged vocabulary sizes, ties (first index wins, bf16 makes
+    plenty), a strided view, -inf rows, and NaN counting as the maximum."""
+    from spikeinfer_b200 import kernels
+    g = torch.Generator().manual_seed(7)
+    for rows, cols in ((1, 1), (3, 17), (64, 151936), (5, 4097)):
+        x = torch.randn(rows, cols, generator=g).to(dtype).to(dev)
+        assert torch.equal(kernels.argmax_rows(x), x.argmax(dim=-1))
+    x = torch.randn(8, 5000, generator=g).to(dtype).to(dev)
+    x[0] = 1.5                      # all equal: index 0
+    x[1, 4000:] = 99.0              # a plateau: its first element
+    x[2] = float("-inf")            # nothing beats the first element
+    x[3, 777] = float("nan")        # NaN is the maximum
+    x[4, 12] = float("nan"); x[4, 4900] = float("nan")
+    want = x.argmax(dim=-1)
+    assert want[:5].tolist() == [0, 4000, 0, 777, 12]
+    assert torch.equal(kernels.argmax_rows(x), want)
+    wide = torch.randn(6, 9000, generator=g).to(dtype).to(dev)
+    view = wide[:, :7001]           # row stride 9000, 7001 columns
+    out = torch.empty(6, dtype=torch.int64, device=dev)
+    ws = torch.empty(kernels.argmax_workspace_bytes(6), dtype=torch.uint8, device=dev)
+    assert kernels.argmax_rows(view, out=out, workspace=ws) is out
+    assert torch.equal(out, view.argmax(dim=-1))
+    with pytest.raises(ValueError):
+        kernels.argmax_rows(wide.t())
