@@ -28,6 +28,8 @@ class SpikeDecodeEngine:
         self.block_size = block_size
         self.max_num_seqs = max_num_seqs
         self.max_blocks = -(-max_model_len // block_size)
+        if model.rope_table is None or model.rope_table.shape[0] < self.max_blocks * block_size:
+            model.build_rope_table(self.max_blocks * block_size)
         self.cache = PagedSpikeCache(c.num_hidden_layers, c.T, c.num_key_value_heads, c.head_dim, num_blocks,
                                      block_size, device=self.device)
         self.state = DecodeBatchState(max_num_seqs, self.max_blocks, num_blocks, block_size, device=self.device)

@@ -106,6 +106,7 @@ class SpikingQwenModel:
             ))
         half = torch.arange(0, c.head_dim, 2, dtype=torch.int64, device=self.device).to(torch.float32)
         self.inv_freq = 1.0 / (c.rope_theta ** (half / c.head_dim))
+        self.rope_table: torch.Tensor | None = None
 
     def validate_thresholds(self) -> bool:
         """threshold > 0 at every LIF site (checked once at load, never per call)."""
@@ -123,10 +124,24 @@ class SpikingQwenModel:
             torch.distributed.all_reduce(partial, group=self.tp_group)
         return partial
 
-    def rope(self, positions: torch.Tensor):
+    def _rope_direct(self, positions: torch.Tensor):
         freqs = positions.to(torch.float32)[:, None] * self.inv_freq[None, :]
         emb = torch.cat((freqs, freqs), dim=-1)
         return emb.cos().to(self.dtype), emb.sin().to(self.dtype)
+
+    def build_rope_table(self, max_positions: int) -> None:
+        """Tabulate the rotary factors of positions ``0 .. max_positions - 1`` with the very operations
+        :meth:`rope` would run per step, so that a step needs one gather instead of seven small launches and
+        gets bit-identical factors.  Positions beyond the table must not be fed afterwards."""
+        cos, sin = self._rope_direct(torch.arange(max_positions, device=self.device))
+        self.rope_table = torch.stack((cos, sin), dim=1).contiguous()  # [max_positions, 2, head_dim]
+
+    def rope(self, positions: torch.Tensor):
+        """``(cos, sin)``, each ``[n_tok, head_dim]`` in the model dtype (rows may be strided)."""
+        if self.rope_table is not None:
+            rows = self.rope_table.index_select(0, positions)
+            return rows[:, 0], rows[:, 1]
+        return self._rope_direct(positions)
 
     @torch.no_grad()
     def forward_paged(self, input_ids, positions, kv_caches, meta: AttentionMetadata, T: int | None = None):
