@@ -71,3 +71,12 @@ def test_host_side_argument_checks(lib):
     wide = big[:-5] + (1.0, None, 0, None, None)
     assert lib.spk_attn_decode(*wide) == -6
     assert lib.spk_meta_advance(1, 1, 1, 1, 1, 1, 1, 1, None, 2048, 4, 0, 16, None, None) == -2
+    # greedy sampling: shape, dtype, null and workspace checks happen before any launch
+    assert lib.spk_argmax_workspace_bytes(0) == 0 and lib.spk_argmax_workspace_bytes(64) == 64 * 16 * 12
+    assert lib.spk_argmax(1, _lib.BF16, 4, 0, 8, 1, 1, 1 << 20, None) == -2         # no columns
+    assert lib.spk_argmax(1, _lib.BF16, 4, 16, 8, 1, 1, 1 << 20, None) == -2        # row stride below the width
+    assert lib.spk_argmax(1, _lib.U8, 4, 16, 16, 1, 1, 1 << 20, None) == -1         # dtype
+    assert lib.spk_argmax(None, _lib.F32, 0, 16, 16, None, None, 0, None) == 0      # no rows: nothing to do
+    assert lib.spk_argmax(None, _lib.F32, 4, 16, 16, 1, 1, 1 << 20, None) == -4     # null logits
+    assert lib.spk_argmax(1, _lib.F32, 4, 16, 16, 1, None, 0, None) == -5           # workspace missing
+    assert lib.spk_argmax(1, _lib.F32, 70000, 16, 16, 1, 1, 1 << 30, None) == -7    # more rows than a grid dimension
