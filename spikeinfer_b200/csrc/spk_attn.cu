@@ -27,11 +27,13 @@
 //    unit is the limit (halving the MMAs as a timing probe, dropping a third of the integer operations,
 //    a quarter of the shared-memory traffic or doubling the resident warps each moved the time by
 //    -3 % .. +20 %); the kernel is bound by dependency latency within a warp's tile.
-#include "spk_common.cuh"
+#include "spk_attn.cuh"
+
+#include <cstdlib>
 
 namespace {
 
-constexpr int kHeads = 8;             // query heads per pass: rows 0..7 (hi) and 8..15 (lo) of the MMA tile
+constexpr int kHeads = kAttnHeads;    // query heads per pass: rows 0..7 (hi) and 8..15 (lo) of the MMA tile
 constexpr int kMaxSplits = 256;
 #ifndef SPK_ATTN_CHUNK_MAX
 #define SPK_ATTN_CHUNK_MAX 4096
@@ -49,22 +51,6 @@ constexpr int kScaleLog2 = 14;
 constexpr float kMaxExponentRange = 24.0f;  // head_dim * scale above this is refused
 constexpr int kLutStride = 2 * 129 + 6;       // words between the fp16-pair tables and their fp32 twins
 constexpr float kLoUnscale = 1.0f / 2048.0f;  // the lo half of a weight is stored times 2^11
-
-struct AttnParams {
-    const uint32_t* q; int64_t sq_t, sq_n, sq_h;
-    const uint32_t* k; int64_t sk_t, sk_h; int sk_blk, sk_slot;  // page and slot strides fit 31 bits (host-checked)
-    const uint32_t* v; int64_t sv_t, sv_h; int sv_blk, sv_slot;
-    const int32_t* tables; int64_t sbt_n;
-    const int32_t* lens;
-    void* out; int out_dtype; int64_t so_t, so_n, so_h;
-    int T; int64_t n_seqs; int Hq, Hkv, n_rep, passes;
-    int bs_log2; int max_keys, num_blocks;  // max_keys = max_blocks * block_size, below 2^31 (host-checked)
-    float scale;
-    float* ws; int splits; int granule;  // granule: keys per CTA step = 32 x warps per CTA
-    int longest_first;  // rank rows by length in-kernel (only worth its dependent load when CTAs outnumber the slots)
-    uint32_t* status;
-    int64_t items;
-};
 
 struct Plan {
     int passes;   // passes per KV head (eight query heads each)
@@ -626,9 +612,22 @@ extern "C" int64_t spk_attn_decode_workspace_bytes(int T, int64_t n_seqs, int nu
         head_dim > 128 || head_dim % 32 != 0 || num_q_heads % num_kv_heads != 0 ||
         log2_exact(block_size) < 0 || max_blocks < 1)
         return 0;
+    // enough for whichever form of the kernel the call takes
     const Plan pl = make_plan(T, n_seqs, num_q_heads, num_kv_heads, head_dim, block_size, max_blocks);
-    if (pl.splits == 1) return 0;
-    return n_seqs * T * num_kv_heads * pl.passes * pl.splits * pl.rec * static_cast<int64_t>(sizeof(float));
+    const int64_t general = pl.splits == 1 ? 0
+        : n_seqs * T * num_kv_heads * pl.passes * pl.splits * pl.rec * static_cast<int64_t>(sizeof(float));
+    const StreamPlan spl = spk_attn_stream_plan(T, n_seqs, num_q_heads, num_kv_heads, head_dim, block_size, max_blocks);
+    const int64_t streaming = spl.ok ? spl.ws_bytes : 0;
+    return general > streaming ? general : streaming;
+}
+
+// SPK_ATTN_FORM=general in the environment keeps every call on the general form (for timing one against the other).
+static bool general_form_forced() {
+    static const bool forced = [] {
+        const char* e = std::getenv("SPK_ATTN_FORM");
+        return e != nullptr && e[0] == 'g';
+    }();
+    return forced;
 }
 
 extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int64_t sq_h,
@@ -662,7 +661,6 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
     const Plan pl = make_plan(T, n_seqs, num_q_heads, num_kv_heads, head_dim, block_size, max_blocks);
     const int64_t need = pl.splits == 1 ? 0
         : n_seqs * T * num_kv_heads * pl.passes * pl.splits * pl.rec * static_cast<int64_t>(sizeof(float));
-    if (need > 0 && (workspace == nullptr || workspace_bytes < need)) return SPK_ERR_WORKSPACE_TOO_SMALL;
 
     AttnParams p;
     p.q = reinterpret_cast<const uint32_t*>(q); p.sq_t = sq_t; p.sq_n = sq_n; p.sq_h = sq_h;
@@ -680,9 +678,18 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
     // global load off the start of every CTA
     p.longest_first = n_seqs > 1 && n_seqs <= 128 && p.items > 148LL * (kSmWarps / pl.warps);
 
+    cudaStream_t s = spk_stream(stream);
+    // Pages of contiguous, 16-byte aligned rows at head_dim 64 / 128 take the streaming form.
+    const StreamPlan spl = spk_attn_stream_plan(T, n_seqs, num_q_heads, num_kv_heads, head_dim, block_size, max_blocks);
+    if (spl.ok && !general_form_forced() && spk_attn_stream_layout_ok(p, head_dim)) {
+        if (spl.ws_bytes > 0 && (workspace == nullptr || workspace_bytes < spl.ws_bytes)) return SPK_ERR_WORKSPACE_TOO_SMALL;
+        p.passes = spl.passes;
+        return spk_attn_stream_launch(p, spl, head_dim, s);
+    }
+    if (need > 0 && (workspace == nullptr || workspace_bytes < need)) return SPK_ERR_WORKSPACE_TOO_SMALL;
+
     const int W = head_dim / 32;
     const bool vec = aligned_to(k, sk_t, sk_h, sk_blk, sk_slot, W) && aligned_to(v, sv_t, sv_h, sv_blk, sv_slot, W);
-    cudaStream_t s = spk_stream(stream);
     switch (W) {
         case 1: return launch_attn<1>(p, vec, s);
         case 2: return launch_attn<2>(p, vec, s);

@@ -55,12 +55,14 @@ def test_host_side_argument_checks(lib):
     assert lib.spk_attn_decode(*args(48, 16)) == -6
     assert lib.spk_attn_decode(*args(64, 12)) == -6
     assert lib.spk_attn_decode(*args(256, 16)) == -6
-    # split-KV plan: rows are cut into key ranges only while the batch alone leaves SMs idle.  64 sequences
-    # (BASELINE config 2) fill the GPU: no workspace, no combine launch.  8 sequences x 4096 keys are cut.
-    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 1) == 0
-    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 256) == 0
-    ws = lib.spk_attn_decode_workspace_bytes(4, 8, 14, 2, 64, 16, 256)
+    # workspace = partial records of rows cut into 512-key units: none while a row cannot exceed one unit;
+    # 64 sequences of up to 4096 keys (the kernel-level attention configuration): 8 units per row, one record
+    # per (sequence, timestep, KV head, unit).
     record = (8 * 64 + 8) * 4                    # eight heads x 64 sums + 8 totals, fp32
+    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 1) == 0
+    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 32) == 0
+    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 256) == 64 * 4 * 2 * 8 * record
+    ws = lib.spk_attn_decode_workspace_bytes(4, 8, 14, 2, 64, 16, 256)
     assert ws > 0 and ws % (8 * 4 * 2 * record) == 0
     assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 48, 16, 256) == 0
     # workspace required but missing -> rejected on the host, nothing launched

@@ -25,6 +25,13 @@ def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
     return ((got.float() - want.float()).abs().max() / scale).item()
 
 
+def within_bf16_bar(got16: torch.Tensor, want: torch.Tensor) -> bool:
+    """16-bit output: within 1e-3 of the largest magnitude before rounding, plus the rounding to bf16 itself
+    (half a step of the value, 2^-9 relative; 2^-8 allows the step a 1e-3 difference can push a value over)."""
+    scale = want.abs().max().clamp(min=1e-6)
+    return bool(((got16.float() - want).abs() <= REL_TOL_BF16 * scale + want.abs() * 2.0 ** -8).all())
+
+
 def run(case, dev, **kw):
     return kernels.paged_spike_attn_decode(**to_dev(case, dev), **kw)
 
@@ -186,7 +193,7 @@ def test_config2_full_size(dev):
     want = orc.paged_spike_attn_decode(**case)
     assert rel_err(got.cpu(), want) < REL_TOL
     got16 = kernels.paged_spike_attn_decode(**d, dtype=torch.bfloat16).cpu()
-    assert rel_err(got16, want.to(torch.bfloat16)) < 2.0 ** -8 + REL_TOL_BF16
+    assert within_bf16_bar(got16, want)
     mask = torch.tensor([0x0F0F0F0F, 0x33333333], dtype=torch.int32, device=dev)
     d1, d2 = dict(d), dict(d)
     d1["v_cache"] = d["v_cache"] & mask
