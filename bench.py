@@ -151,6 +151,15 @@ def random_weights_device(cfg, device, dtype, seed: int) -> dict:
     return w
 
 
+def model_len(total_steps: int) -> int:
+    """max_model_len of the workload: prompt + every decode step the run will take, rounded up to 256."""
+    return -(-(PROMPT_LEN + total_steps + 2 * BLOCK_SIZE) // 256) * 256
+
+
+def total_decode_steps(K: int, W: int) -> int:
+    return 2 * (K + W) + 8  # device-timed and host-in-the-loop passes, plus slack
+
+
 def build_engine(device, seed: int, total_steps: int, rank: int = 0, world: int = 1):
     """0.5B-shape model, calibrated thresholds, 64 requests prefilled, decode graph captured."""
     from spikeinfer_b200 import _lib
@@ -170,8 +179,7 @@ def build_engine(device, seed: int, total_steps: int, rank: int = 0, world: int 
     prompts = all_prompts[mine.start:mine.stop]
     rates = calibrate_thresholds(model, prompts[:8].to(device))
     model.validate_thresholds()
-    max_len = PROMPT_LEN + total_steps + 2 * BLOCK_SIZE
-    max_len = -(-max_len // 256) * 256
+    max_len = model_len(total_steps)
     blocks_per_seq = -(-max_len // BLOCK_SIZE)
     engine = SpikeDecodeEngine(model, num_blocks=N_REQ * blocks_per_seq + 1, block_size=BLOCK_SIZE,
                                max_num_seqs=N_REQ, max_model_len=max_len)
@@ -351,6 +359,7 @@ def cpu_baseline(steps: int = 3, warmup: int = 1) -> dict:
 
 # --------------------------------------------------------------------------- arms
 def config_dict(world: int, max_len) -> dict:
+    # identical in both arms: the reference arm times ONE replica's 64 requests on the host's cores whatever N is
     return {"workload": "decode_0p5b_64req: spiking Qwen2.5-0.5B shape, T=4, bf16, 64 concurrent requests per GPU, "
                         "128-token prompts, greedy decode, page 16, CUDA-graph decode step",
             "requests_per_gpu": N_REQ, "prompt_len": PROMPT_LEN, "block_size": BLOCK_SIZE, "max_model_len": max_len,
@@ -375,7 +384,7 @@ def run_own(args) -> None:
         torch.cuda.synchronize(device)
 
     K, W = args.steps, max(args.warmup, 3)
-    engine, rates, launches_per_step, max_len = build_engine(device, seed=1234, total_steps=2 * (K + W) + 8,
+    engine, rates, launches_per_step, max_len = build_engine(device, seed=1234, total_steps=total_decode_steps(K, W),
                                                              rank=rank, world=world)
 
     # ---- value: tokens stay on the device --------------------------------
@@ -440,17 +449,25 @@ def run_reference(args) -> None:
     rank, world, _ = dist_info()
     if rank != 0:
         return
-    K, W = args.steps, max(args.warmup, 1)
-    sample = CpuDecodeSample(max_len=-(-(PROMPT_LEN + K + W + 16) // 256) * 256)
-    sec = time_cpu_steps(sample, K, W)
+    # One host has one set of cores: the CPU arm is ONE replica's 64 requests on all of them, whatever N is
+    # (under a multi-rank launcher the other ranks leave at once and the launcher's one-thread default is undone).
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    K = args.steps
+    W = max(args.warmup, 3)  # the same clamp as the own arm, so that both arms print the same max_model_len
+    max_len = model_len(total_decode_steps(K, W))
+    W_cpu = max(min(args.warmup, 2), 1)  # a CPU step takes a third of a second: two warm-up steps settle it
+    sample = CpuDecodeSample(max_len=max_len)
+    sec = time_cpu_steps(sample, K, W_cpu)
     value = round(N_REQ / sec, 2)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": K,
         "warmup": W, "ms_per_step": round(sec * 1e3, 2), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_dict(max(world, 1), None),
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_dict(max(world, 1), max_len),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": "each step = one full decode step of 64 requests at context 128+ on the host "
-                                   "cores (fp32, pools pre-filled with Bernoulli(0.15) bits instead of a CPU prefill)"},
+                         "sample": "each step = one full decode step of ONE replica's 64 requests at context 128+ on "
+                                   "all of this host's cores, whatever --gpus is (fp32, pools pre-filled with "
+                                   f"Bernoulli(0.15) bits instead of a CPU prefill; {W_cpu} CPU warm-up steps)"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -525,6 +542,7 @@ def run_tp7b(args) -> None:
     for row, c in enumerate(ctx):
         table = engine.state.take_blocks(-(-c // BLOCK_SIZE))
         engine.state.admit(row, table, c, row % cfg.vocab_size)
+        engine.ledger.admit(row, c)
     engine.free_rows = []
     torch.cuda.synchronize(device)
     stage("pools filled, rows admitted")

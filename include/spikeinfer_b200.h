@@ -69,7 +69,9 @@ enum {
     SPK_STATUS_BAD_SEQ_LEN = 1u << 1,   /* seq_len < 1 or > max_blocks * block_size         */
     SPK_STATUS_BAD_SLOT = 1u << 2,      /* slot_mapping entry outside [0, num_slots)        */
     SPK_STATUS_POOL_EXHAUSTED = 1u << 3,/* metadata builder ran out of free blocks          */
-    SPK_STATUS_TABLE_FULL = 1u << 4     /* a row needs more than max_blocks blocks          */
+    SPK_STATUS_TABLE_FULL = 1u << 4,    /* a row needs more than max_blocks blocks          */
+    SPK_STATUS_FREE_LIST_OVERFLOW = 1u << 5, /* a release would push past the list's capacity    */
+    SPK_STATUS_ROW_BUSY = 1u << 6       /* admit into a row that still holds a sequence      */
 };
 
 /* Library version, (major << 16) | (minor << 8) | patch. */
@@ -204,17 +206,18 @@ int spk_argmax(const void* x, int dtype, int64_t rows, int64_t cols, int64_t row
  * out      [T, n_seqs, H_q, head_dim] in out_dtype (F32/BF16/F16), strides so_t, so_n,
  *          so_h (channel stride 1) -- may be a view of a larger buffer.
  *
- * scores are exact integers popc(q & k); the softmax weights are carried as pairs of
- * fp16 numbers (22 significant bits) and the weighted sum p.v runs on the tensor cores
- * with fp32 accumulation (within 1e-6 of a float64 evaluation, relative to the largest
- * output).  K and V are read once per KV head, shared by the H_q/H_kv query heads of
- * the group.  When the batch alone cannot fill the GPU, rows are split into key ranges
- * whose partial sums live in `workspace` (size from spk_attn_decode_workspace_bytes with
- * the same arguments; may be NULL when that returns 0).  head_dim must be a multiple of
- * 32, <= 128; block_size a power of two, >= 1; 0 <= scale and scale * head_dim <= 24
- * (head_dim^-0.5, the reference's scale, always is), else SPK_ERR_UNSUPPORTED;
- * max_blocks * block_size, num_blocks and the block/slot strides must fit 31 bits, else
- * SPK_ERR_TOO_LARGE.
+ * scores are exact integers popc(q & k); the weighted sum p.v runs on the tensor cores with
+ * fp32 accumulation.  For F32 output the softmax weights are carried as pairs of fp16 numbers
+ * (22 significant bits; within 1e-6 of a float64 evaluation, relative to the largest output);
+ * for BF16/F16 output one fp16 weight is used in numerator and denominator alike (within 1e-3
+ * before the rounding to the output type).  K and V are read once per KV head, shared by the
+ * H_q/H_kv query heads of the group.  Rows are cut into key ranges (512-key units when pages are
+ * contiguous 16-byte aligned rows at head_dim 64/128) whose partial sums live in `workspace`
+ * (size from spk_attn_decode_workspace_bytes with the same arguments; may be NULL when that
+ * returns 0).  head_dim must be a multiple of 32, <= 128; block_size a power of two, >= 1;
+ * 0 <= scale and scale * head_dim <= 24 (head_dim^-0.5, the reference's scale, always is), else
+ * SPK_ERR_UNSUPPORTED; max_blocks * block_size + 800, num_blocks and the block/slot strides
+ * must fit 31 bits, else SPK_ERR_TOO_LARGE.
  * ------------------------------------------------------------------------- */
 int64_t spk_attn_decode_workspace_bytes(int T, int64_t n_seqs, int num_q_heads, int num_kv_heads,
                                         int head_dim, int block_size, int64_t max_blocks);
@@ -239,13 +242,18 @@ int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int64_t sq_h,
  *
  *  - No cudaMalloc / cudaFree and no other allocating call is made, here or on first use.
  *  - A problem whose spk_attn_decode_workspace_bytes() exceeds spk_attn_decode_static_capacity()
- *    is refused with SPK_ERR_STATIC_SCRATCH_TOO_SMALL and nothing is launched (64 sequences of up
- *    to 4096 keys at T=4, 14/2 heads, head_dim 64 need 7.5 MB and fit).
- *  - The first call on each device looks up the array's device address (with that device current)
- *    and remembers it; make that first call during start-up, before any stream capture begins.
+ *    is refused with SPK_ERR_STATIC_SCRATCH_TOO_SMALL and nothing is launched.  Sequences of up to
+ *    512 keys need no scratch at all; 48 sequences of up to 4096 keys at T=4, 14/2 heads,
+ *    head_dim 64 need 6.4 MB (one 2080-byte record per sequence, timestep, KV head and 512-key unit)
+ *    and fit, 64 such sequences (8.5 MB) do not.
+ *  - The first call on each device, whatever its sizes (a problem that needs no scratch included),
+ *    looks up the array's device address with that device current and remembers it; make that
+ *    first call during start-up, before any stream capture begins.  Later calls only read the
+ *    remembered address.
  *  - All calls on a device share the one array and it keeps whatever the last call wrote.  Nothing
  *    in it has to start at zero (each call writes every record it later reads), but two calls
- *    whose kernels overlap on the GPU, e.g. on different streams, race on it: serialise them. */
+ *    whose kernels overlap on the GPU, e.g. on different streams, race on it: one call at a time
+ *    per device. */
 #define SPK_ATTN_STATIC_SCRATCH_BYTES (8ll << 20)
 int64_t spk_attn_decode_static_capacity(void);
 int spk_attn_decode_static(const int32_t* q, int64_t sq_t, int64_t sq_n, int64_t sq_h,
@@ -313,26 +321,29 @@ int spk_meta_advance(int32_t* free_list, int32_t* free_count, const int32_t* act
                      uint32_t* status, void* stream);
 
 /* Install a prefilled sequence in `row`: its first ceil(seq_len / bs) table entries are copied from
- * src_table (device int32), the rest of the row is the pad block; the blocks are assumed to be
- * already removed from the free list by spk_meta_take (or by a host mirror).  last_token, the token
- * sampled after prefill, becomes input_ids[row] and, when next_tokens != NULL, next_tokens[row], so
- * that the following spk_meta_advance feeds it to the model. */
+ * src_table (device int32), the rest of the row is the pad block; the blocks must have been removed
+ * from the free list by spk_meta_take.  last_token, the token sampled after prefill, becomes
+ * input_ids[row] and, when next_tokens != NULL, next_tokens[row], so that the following
+ * spk_meta_advance feeds it to the model.  A row that is still active is left as it is and
+ * SPK_STATUS_ROW_BUSY is set (overwriting it would leak its blocks). */
 int spk_meta_admit(int32_t row, const int32_t* src_table, int32_t seq_len, int64_t last_token,
                    int32_t* active, int32_t* seq_lens, int64_t* positions, int64_t* slot_mapping,
                    int32_t* block_tables, int64_t* input_ids, int64_t* next_tokens,
                    int32_t max_rows, int32_t max_blocks, int32_t pad_block, int32_t block_size,
-                   void* stream);
+                   uint32_t* status, void* stream);
 
 /* Pop `count` blocks for a new sequence into dst_table[0..count) (allocation order = pop order). */
 int spk_meta_take(int32_t* free_list, int32_t* free_count, int32_t count, int32_t* dst_table,
                   uint32_t* status, void* stream);
 
 /* Finish `row`: push its ceil(seq_len / bs) blocks back in table order
- * (block_manager.py:63-66), reset the row to the pad state. */
+ * (block_manager.py:63-66), reset the row to the pad state.  num_alloc_blocks is the capacity of
+ * free_list: a push that would pass it is skipped and SPK_STATUS_FREE_LIST_OVERFLOW is set. */
 int spk_meta_release(int32_t row, int32_t* free_list, int32_t* free_count, int32_t* active,
                      int32_t* seq_lens, int64_t* positions, int64_t* slot_mapping,
                      int32_t* block_tables, int32_t max_rows, int32_t max_blocks,
-                     int32_t pad_block, int32_t block_size, void* stream);
+                     int32_t pad_block, int32_t block_size, int32_t num_alloc_blocks,
+                     uint32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -22,6 +22,8 @@ STATUS_BAD_SEQ_LEN = 1 << 1
 STATUS_BAD_SLOT = 1 << 2
 STATUS_POOL_EXHAUSTED = 1 << 3
 STATUS_TABLE_FULL = 1 << 4
+STATUS_FREE_LIST_OVERFLOW = 1 << 5
+STATUS_ROW_BUSY = 1 << 6
 
 MAX_LIF_SITES = 4
 
@@ -128,10 +130,10 @@ SIGNATURES = {
                                  c_void_p]),
     "spk_meta_admit": (c_int, [c_int32, c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
-                               c_int32, c_void_p]),
+                               c_int32, c_void_p, c_void_p]),
     "spk_meta_take": (c_int, [c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p]),
     "spk_meta_release": (c_int, [c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                 c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+                                 c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
 }
 
 _lib = None

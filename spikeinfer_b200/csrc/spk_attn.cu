@@ -29,6 +29,7 @@
 //    -3 % .. +20 %); the kernel is bound by dependency latency within a warp's tile.
 #include "spk_attn.cuh"
 
+#include <atomic>
 #include <cstdlib>
 
 namespace {
@@ -487,7 +488,7 @@ attn_combine_kernel(const AttnParams p, int D) {
     if (len < 1) len = 0;
     if (len > p.max_keys) len = p.max_keys;
     const int range = row_range_keys(len, p.splits, p.granule);
-    const int n_splits = static_cast<int>((len + range - 1) / range);
+    const int n_splits = (len > 0 && range > 0) ? (len + range - 1) / range : 0;  // an empty row has no records
     const int64_t rec_floats = static_cast<int64_t>(kHeads) * D + 8;
     const float* base = p.ws + grp_item * p.splits * rec_floats;
     for (int idx = threadIdx.x; idx < nh * D; idx += blockDim.x) {
@@ -610,7 +611,8 @@ extern "C" int64_t spk_attn_decode_workspace_bytes(int T, int64_t n_seqs, int nu
                                                    int64_t max_blocks) {
     if (T < 1 || n_seqs < 1 || num_q_heads < 1 || num_kv_heads < 1 || head_dim < 32 ||
         head_dim > 128 || head_dim % 32 != 0 || num_q_heads % num_kv_heads != 0 ||
-        log2_exact(block_size) < 0 || max_blocks < 1)
+        log2_exact(block_size) < 0 || max_blocks < 1 ||
+        max_blocks > (0x7fffffffLL - 3 * 256 - 32) / block_size)  // spk_attn_decode refuses these
         return 0;
     // enough for whichever form of the kernel the call takes
     const Plan pl = make_plan(T, n_seqs, num_q_heads, num_kv_heads, head_dim, block_size, max_blocks);
@@ -652,9 +654,10 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
         seq_lens == nullptr || out == nullptr)
         return SPK_ERR_NULL_POINTER;
 
-    // the kernel indexes keys, pages and the page/slot strides with 32-bit integers
+    // the kernel indexes keys, pages and the page/slot strides with 32-bit integers; it forms key indices up to
+    // two CTA steps and a tile past a row's end (prefetch), so the largest row stays that far below 2^31
     const int64_t lim = 0x7fffffffLL;
-    if (max_blocks > (lim >> bs_log2) - 8 || num_blocks > lim) return SPK_ERR_TOO_LARGE;
+    if ((max_blocks << bs_log2) > lim - 3 * 256 - 32 || max_blocks > lim || num_blocks > lim) return SPK_ERR_TOO_LARGE;
     for (int64_t st : {sk_blk, sk_slot, sv_blk, sv_slot})
         if (st > lim || st < -lim) return SPK_ERR_TOO_LARGE;
 
@@ -771,7 +774,9 @@ constexpr int64_t kStaticScratchBytes = SPK_ATTN_STATIC_SCRATCH_BYTES;
 static __device__ __align__(256) float g_attn_static_scratch[kStaticScratchBytes / sizeof(float)];
 
 constexpr int kMaxDevices = 64;
-static float* g_static_scratch_ptr[kMaxDevices] = {};  // per device, filled on first use
+// per device, filled on first use; atomic because any host thread may make that first call (two threads
+// racing store the same value)
+static std::atomic<float*> g_static_scratch_ptr[kMaxDevices];
 
 // Device address of the array on the current device.  The array's name is only a host-side handle:
 // the address a kernel can use has to be asked for, once per device, with that device current.
@@ -780,13 +785,15 @@ static int static_scratch_for_current_device(float** out) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return spk_set_cuda_error(e);
     if (dev < 0 || dev >= kMaxDevices) return SPK_ERR_UNSUPPORTED;
-    if (g_static_scratch_ptr[dev] == nullptr) {
+    float* known = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (known == nullptr) {
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
         if (e != cudaSuccess) return spk_set_cuda_error(e);
-        g_static_scratch_ptr[dev] = static_cast<float*>(p);
+        known = static_cast<float*>(p);
+        g_static_scratch_ptr[dev].store(known, std::memory_order_release);
     }
-    *out = g_static_scratch_ptr[dev];
+    *out = known;
     return SPK_OK;
 }
 
@@ -803,11 +810,11 @@ extern "C" int spk_attn_decode_static(const int32_t* q, int64_t sq_t, int64_t sq
     const int64_t need = spk_attn_decode_workspace_bytes(T, n_seqs, num_q_heads, num_kv_heads, head_dim,
                                                          block_size, max_blocks);
     if (need > kStaticScratchBytes) return SPK_ERR_STATIC_SCRATCH_TOO_SMALL;
+    // The address is looked up on the first call per device whatever the problem needs, so that a small
+    // warm-up call at start-up settles it and no later call (possibly inside a stream capture) has to.
     float* scratch = nullptr;
-    if (need > 0) {
-        const int rc = static_scratch_for_current_device(&scratch);
-        if (rc != SPK_OK) return rc;
-    }
+    const int rc = static_scratch_for_current_device(&scratch);
+    if (rc != SPK_OK) return rc;
     // Every partial record the combine pass reads is written earlier in the same call, so the
     // array needs no clearing between calls; whatever the previous call left is never read.
     return spk_attn_decode(q, sq_t, sq_n, sq_h, k, sk_t, sk_h, sk_blk, sk_slot, v, sv_t, sv_h, sv_blk, sv_slot,

@@ -120,7 +120,14 @@ __global__ void meta_admit_kernel(int32_t row, const int32_t* src_table, int32_t
                                   int64_t last_token, int32_t* active, int32_t* seq_lens,
                                   int64_t* positions, int64_t* slot_mapping, int32_t* tables,
                                   int64_t* input_ids, int64_t* next_tokens, int32_t max_blocks,
-                                  int32_t pad_block, int32_t block_size) {
+                                  int32_t pad_block, int32_t block_size, uint32_t* status) {
+    // a row that still holds a sequence keeps it: overwriting its table would leak its blocks
+    const bool busy = active[row] != 0;
+    __syncthreads();
+    if (busy) {
+        if (threadIdx.x == 0) spk_flag(status, SPK_STATUS_ROW_BUSY);
+        return;
+    }
     const int nb = (seq_len + block_size - 1) / block_size;
     for (int i = threadIdx.x; i < max_blocks; i += blockDim.x)
         tables[static_cast<int64_t>(row) * max_blocks + i] = i < nb ? src_table[i] : pad_block;
@@ -137,12 +144,19 @@ __global__ void meta_admit_kernel(int32_t row, const int32_t* src_table, int32_t
 __global__ void meta_release_kernel(int32_t row, int32_t* free_list, int32_t* free_count,
                                     int32_t* active, int32_t* seq_lens, int64_t* positions,
                                     int64_t* slot_mapping, int32_t* tables, int32_t max_blocks,
-                                    int32_t pad_block, int32_t block_size) {
+                                    int32_t pad_block, int32_t block_size, int32_t num_alloc,
+                                    uint32_t* status) {
     const int fc = *free_count;
     const int len = active[row] != 0 ? seq_lens[row] : 0;
     int nb = (len + block_size - 1) / block_size;
     if (nb > max_blocks) nb = max_blocks;
     __syncthreads();
+    if (fc < 0 || fc + nb > num_alloc) {
+        // more blocks coming back than ever left the list (the count was not kept in step with the
+        // tables): nothing is pushed, the row is still retired
+        if (threadIdx.x == 0) spk_flag(status, SPK_STATUS_FREE_LIST_OVERFLOW);
+        nb = 0;
+    }
     for (int i = threadIdx.x; i < max_blocks; i += blockDim.x) {
         int32_t* e = tables + static_cast<int64_t>(row) * max_blocks + i;
         if (i < nb) free_list[fc + i] = *e;
@@ -209,7 +223,7 @@ extern "C" int spk_meta_admit(int32_t row, const int32_t* src_table, int32_t seq
                               int32_t* active, int32_t* seq_lens, int64_t* positions,
                               int64_t* slot_mapping, int32_t* block_tables, int64_t* input_ids,
                               int64_t* next_tokens, int32_t max_rows, int32_t max_blocks,
-                              int32_t pad_block, int32_t block_size, void* stream) {
+                              int32_t pad_block, int32_t block_size, uint32_t* status, void* stream) {
     if (row < 0 || row >= max_rows || max_blocks < 1 || block_size < 1 || seq_len < 0) return SPK_ERR_BAD_SHAPE;
     if ((static_cast<int64_t>(seq_len) + block_size - 1) / block_size > max_blocks) return SPK_ERR_TOO_LARGE;
     if (src_table == nullptr || active == nullptr || seq_lens == nullptr || positions == nullptr ||
@@ -217,7 +231,7 @@ extern "C" int spk_meta_admit(int32_t row, const int32_t* src_table, int32_t seq
         return SPK_ERR_NULL_POINTER;
     meta_admit_kernel<<<1, 256, 0, spk_stream(stream)>>>(row, src_table, seq_len, last_token, active, seq_lens,
                                                          positions, slot_mapping, block_tables, input_ids,
-                                                         next_tokens, max_blocks, pad_block, block_size);
+                                                         next_tokens, max_blocks, pad_block, block_size, status);
     SPK_CHECK_LAUNCH();
     return SPK_OK;
 }
@@ -225,14 +239,15 @@ extern "C" int spk_meta_admit(int32_t row, const int32_t* src_table, int32_t seq
 extern "C" int spk_meta_release(int32_t row, int32_t* free_list, int32_t* free_count, int32_t* active,
                                 int32_t* seq_lens, int64_t* positions, int64_t* slot_mapping,
                                 int32_t* block_tables, int32_t max_rows, int32_t max_blocks,
-                                int32_t pad_block, int32_t block_size, void* stream) {
-    if (row < 0 || row >= max_rows || max_blocks < 1 || block_size < 1) return SPK_ERR_BAD_SHAPE;
+                                int32_t pad_block, int32_t block_size, int32_t num_alloc_blocks,
+                                uint32_t* status, void* stream) {
+    if (row < 0 || row >= max_rows || max_blocks < 1 || block_size < 1 || num_alloc_blocks < 0) return SPK_ERR_BAD_SHAPE;
     if (free_list == nullptr || free_count == nullptr || active == nullptr || seq_lens == nullptr ||
         positions == nullptr || slot_mapping == nullptr || block_tables == nullptr)
         return SPK_ERR_NULL_POINTER;
     meta_release_kernel<<<1, 256, 0, spk_stream(stream)>>>(row, free_list, free_count, active, seq_lens,
                                                            positions, slot_mapping, block_tables, max_blocks,
-                                                           pad_block, block_size);
+                                                           pad_block, block_size, num_alloc_blocks, status);
     SPK_CHECK_LAUNCH();
     return SPK_OK;
 }

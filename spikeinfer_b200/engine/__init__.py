@@ -1,9 +1,9 @@
-"""Decode-side engine pieces: the paged spike pool, the block allocator and the on-GPU batch state."""
+"""Decode-side engine pieces: the paged spike pool, the on-GPU batch state and its host-side block ledger."""
 from .batch_state import DecodeBatchState
-from .block_manager import BlockManager
+from .block_ledger import BlockLedger
 from .spike_cache import PagedSpikeCache
 
-__all__ = ["DecodeBatchState", "BlockManager", "PagedSpikeCache", "SpikeDecodeEngine"]
+__all__ = ["DecodeBatchState", "BlockLedger", "PagedSpikeCache", "SpikeDecodeEngine"]
 
 
 def __getattr__(name):

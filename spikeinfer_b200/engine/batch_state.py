@@ -65,7 +65,8 @@ class DecodeBatchState:
 
     def take_blocks(self, count: int) -> torch.Tensor:
         """Pop ``count`` blocks from the device free list (allocation order) into a new int32 tensor."""
-        dst = torch.empty(count, dtype=torch.int32, device=self.device)
+        # pad-block filled: if the device list turns out short (status POOL_EXHAUSTED) the entries stay harmless
+        dst = torch.full((count,), self.pad_block, dtype=torch.int32, device=self.device)
         with torch.cuda.device(self.device):
             rc = self._lib.spk_meta_take(self.free_list.data_ptr(), self._free_count.data_ptr(), count,
                                          dst.data_ptr(), self.status.data_ptr(), self._stream())
@@ -82,7 +83,7 @@ class DecodeBatchState:
                 row, table.data_ptr(), seq_len, last_token, self.active.data_ptr(), self.seq_lens.data_ptr(),
                 self.positions.data_ptr(), self.slot_mapping.data_ptr(), self.block_tables.data_ptr(),
                 self.input_ids.data_ptr(), self.next_tokens.data_ptr(), self.max_rows, self.max_blocks,
-                self.pad_block, self.block_size, self._stream())
+                self.pad_block, self.block_size, self.status.data_ptr(), self._stream())
         _lib.check(rc, "spk_meta_admit")
 
     def release(self, row: int) -> None:
@@ -92,7 +93,7 @@ class DecodeBatchState:
                 row, self.free_list.data_ptr(), self._free_count.data_ptr(), self.active.data_ptr(),
                 self.seq_lens.data_ptr(), self.positions.data_ptr(), self.slot_mapping.data_ptr(),
                 self.block_tables.data_ptr(), self.max_rows, self.max_blocks, self.pad_block,
-                self.block_size, self._stream())
+                self.block_size, self.num_blocks - 1, self.status.data_ptr(), self._stream())
         _lib.check(rc, "spk_meta_release")
 
     def free_count(self) -> int:
@@ -106,5 +107,7 @@ class DecodeBatchState:
             self.status.zero_()
             names = [n for n, b in (("bad block", _lib.STATUS_BAD_BLOCK), ("bad seq_len", _lib.STATUS_BAD_SEQ_LEN),
                                     ("bad slot", _lib.STATUS_BAD_SLOT), ("pool exhausted", _lib.STATUS_POOL_EXHAUSTED),
-                                    ("block table full", _lib.STATUS_TABLE_FULL)) if bits & b]
+                                    ("block table full", _lib.STATUS_TABLE_FULL),
+                                    ("free list overflow", _lib.STATUS_FREE_LIST_OVERFLOW),
+                                    ("row busy", _lib.STATUS_ROW_BUSY)) if bits & b]
             raise _lib.SpkError("device status: " + ", ".join(names))

@@ -16,6 +16,7 @@ from ..attention import AttentionMetadata, build_prefill_rows
 from ..kernels import argmax_rows, argmax_workspace_bytes
 from ..modeling import SpikingQwenModel
 from .batch_state import DecodeBatchState
+from .block_ledger import BlockLedger
 from .spike_cache import PagedSpikeCache
 
 
@@ -33,6 +34,7 @@ class SpikeDecodeEngine:
         self.cache = PagedSpikeCache(c.num_hidden_layers, c.T, c.num_key_value_heads, c.head_dim, num_blocks,
                                      block_size, device=self.device)
         self.state = DecodeBatchState(max_num_seqs, self.max_blocks, num_blocks, block_size, device=self.device)
+        self.ledger = BlockLedger(num_blocks - 1, block_size, self.max_blocks)  # host count of the device free list
         self.meta = AttentionMetadata(
             slot_mapping=self.state.slot_mapping, block_size=block_size, num_decode_tokens=max_num_seqs,
             block_tables=self.state.block_tables, seq_lens=self.state.seq_lens, status=self.state.status)
@@ -56,6 +58,11 @@ class SpikeDecodeEngine:
         """Prefill ``prompts`` in one eager batch and install them as decode rows.  Returns the rows."""
         if len(prompts) > len(self.free_rows):
             raise RuntimeError("no free decode row")
+        # admission control before anything is taken from the device list (the reference's scheduler asks
+        # BlockManager.can_allocate first, spikeinfer/engine/scheduler.py:160): nothing is touched on refusal
+        why = self.ledger.admission_error([len(p) for p in prompts])
+        if why is not None:
+            raise RuntimeError(f"cannot admit: {why}")
         bs, dev = self.block_size, self.device
         ids, pos, slot_parts, starts, lens, tables = [], [], [], [], [], []
         for p in prompts:
@@ -82,6 +89,7 @@ class SpikeDecodeEngine:
         for i, (table, n) in enumerate(zip(tables, lens)):
             row = self.free_rows.pop()
             self.state.admit(row, table, n, 0)
+            self.ledger.admit(row, n)
             rows.append(row)
         idx = torch.tensor(rows, dtype=torch.int64, device=dev)
         self.state.next_tokens[idx] = first_tokens
@@ -90,6 +98,7 @@ class SpikeDecodeEngine:
 
     def release(self, row: int) -> None:
         self.state.release(row)
+        self.ledger.release(row)
         self.free_rows.append(row)
 
     # -- decode -----------------------------------------------------------
@@ -133,6 +142,7 @@ class SpikeDecodeEngine:
             self.graph.replay()
         else:
             self._body()
+        self.ledger.advance()
 
     @torch.no_grad()
     def decode_steps(self, k: int) -> torch.Tensor:

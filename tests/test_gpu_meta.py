@@ -73,6 +73,30 @@ def test_pool_exhaustion_and_full_table_are_flagged(dev):
     assert state2.seq_lens[0].item() == 2
 
 
+def test_release_past_capacity_and_admit_into_a_busy_row_are_flagged(dev):
+    """A free count that was not kept in step with the tables must not push past the list; a row that still holds
+    a sequence keeps it."""
+    state = DecodeBatchState(max_rows=2, max_blocks=4, num_blocks=5, block_size=2, device=dev)
+    table = state.take_blocks(2)
+    state.admit(0, table, 4, 7)
+    assert state.free_count() == 2
+    state._free_count.fill_(4)          # host-side injection: pretend nothing was ever taken
+    before = state.free_list.clone()
+    state.release(0)
+    assert state.status.item() & _lib.STATUS_FREE_LIST_OVERFLOW
+    assert torch.equal(state.free_list, before) and state.free_count() == 4, "nothing may be pushed"
+    assert state.active[0].item() == 0, "the row is retired all the same"
+    state.status.zero_()
+    state.reset()
+    t0 = state.take_blocks(1)
+    state.admit(1, t0, 2, 5)
+    row_before = state.block_tables[1].clone()
+    state.admit(1, state.take_blocks(1), 1, 9)   # the row is busy
+    assert state.status.item() & _lib.STATUS_ROW_BUSY
+    assert torch.equal(state.block_tables[1], row_before) and state.seq_lens[1].item() == 2
+    assert state.input_ids[1].item() == 5
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_argmax_rows_matches_torch(dtype, dev):
     """Greedy sampling kernel against torch.argmax: ragged vocabulary sizes, ties (first index wins, bf16 makes

@@ -11,12 +11,14 @@ import torch
 import cases
 from oracle import model_oracle as mo
 from oracle import torch_oracle as orc
-from spikeinfer_b200 import kernels
+from spikeinfer_b200 import _lib, kernels
 from spikeinfer_b200.attention import AttentionMetadata, fused_qkv_attention, paged_attention
 from spikeinfer_b200.engine.decode_engine import SpikeDecodeEngine
 from spikeinfer_b200.modeling import SpikingQwenConfig, SpikingQwenModel
 
 pytestmark = pytest.mark.gpu
+
+POOL_DIFF_BOUND = 0.0  # free-running engine vs CPU oracle, fraction of a layer's cached bits: measured 0 on B200
 
 
 def tiny_prompts(vocab):
@@ -120,12 +122,50 @@ def test_engine_tokens_match_reference(variant, use_graph, packed_prefill, dev, 
     run.prefill(tiny_prompts(shape.vocab_size))
     for _ in range(15):
         run.decode()
+    worst = 0.0
     for i in range(shape.num_hidden_layers):
         for pool, want in ((eng.cache.k[i], run.k[i]), (eng.cache.v[i], run.v[i])):
             got = pool.cpu()
             pad = slice(eng.cache.pad_slot, None)
             diff = (orc.unpack_spikes(got[:, :, :pad.start], 64) != orc.unpack_spikes(want[:, :, :pad.start], 64)).float().mean().item()
-            assert diff <= 1e-3, f"layer {i}: {diff:.2e} of cached bits differ from the CPU run"
+            worst = max(worst, diff)
+    # Free-running (not teacher-forced) the GPU's GEMMs sum in another order than the CPU's, so a current that
+    # lands within an ulp of its threshold could spike on one side only; on B200 none does (all 64 tokens
+    # match and every cached bit equals the CPU run's), so the bound is exact equality.
+    print(f"largest fraction of cached bits differing from the CPU run: {worst:.3e}")
+    assert worst <= POOL_DIFF_BOUND, f"{worst:.2e} of a layer's cached bits differ from the CPU run"
+
+
+def test_admission_control_and_block_ledger(dev, golden):
+    """Over-admission raises before anything is taken from the device list and leaves pools, tables and the free
+    list untouched; the host ledger's free count equals the device's after prefill, decode steps and a release."""
+    g, shape, w = build(golden, "constant_lif")
+    model = SpikingQwenModel(SpikingQwenConfig(**g["config"]), w, device=dev)
+    # 7 allocatable blocks of 16 tokens: four 32-token prompts need 8
+    eng = SpikeDecodeEngine(model, num_blocks=8, block_size=16, max_num_seqs=4, max_model_len=64, use_graph=False)
+    prompts = tiny_prompts(shape.vocab_size)
+    pools = [t.clone() for kv in eng.cache.layers for t in kv]
+    free_before = eng.state.free_list.clone()
+    with pytest.raises(RuntimeError, match="need 8 blocks, 7 are free"):
+        eng.add_requests(prompts)
+    with pytest.raises(RuntimeError, match="exceeds max_model_len"):
+        eng.add_requests([list(range(65))])
+    assert eng.state.free_count() == 7 and torch.equal(eng.state.free_list, free_before)
+    assert all(torch.equal(a, b) for a, b in zip(pools, [t for kv in eng.cache.layers for t in kv]))
+    assert eng.state.status.item() == 0 and len(eng.free_rows) == 4 and int(eng.state.active.sum()) == 0
+    rows = eng.add_requests(prompts[:3])          # 6 blocks
+    assert eng.ledger.free == eng.state.free_count() == 1
+    eng.decode_step()                             # all three rows sit on a page boundary: one gets the block
+    assert eng.ledger.free == eng.state.free_count() == 0
+    assert eng.state.status.item() & _lib.STATUS_POOL_EXHAUSTED
+    assert eng.state.seq_lens[:3].tolist() == [33, 32, 32] == [eng.ledger.seq_lens[r] for r in rows]
+    eng.state.status.zero_()
+    eng.release(rows[0])
+    assert eng.ledger.free == eng.state.free_count() == 3
+    eng.decode_step()
+    assert eng.ledger.free == eng.state.free_count() == 1
+    assert eng.state.seq_lens[1:3].tolist() == [33, 33]
+    eng.state.check_status()
 
 
 def test_host_in_the_loop_step(dev, golden):

@@ -103,3 +103,40 @@ def test_build_prefill_rows_turns_chunks_into_decode_rows():
     # no prefill chunks: nothing to do
     none = AttentionMetadata(slot_mapping=torch.zeros(1, dtype=torch.int64), block_size=4, num_decode_tokens=1)
     assert build_prefill_rows(none).prefill_row_tables is None
+
+
+def test_block_ledger_counts_follow_the_allocation_rules():
+    """The host ledger moves as many blocks as the device does: ceil(len / bs) at admission, one per row on a
+    page boundary per step (row order, none when the list is empty or the table is full), all back at release."""
+    from spikeinfer_b200.engine.block_ledger import BlockLedger
+    led = BlockLedger(num_alloc_blocks=6, block_size=4, max_blocks_per_seq=3)
+    assert led.admission_error([5, 4]) is None
+    assert "exceeds max_model_len" in led.admission_error([13])
+    assert "need 7 blocks" in led.admission_error([12, 12, 4])
+    assert "empty prompt" in led.admission_error([0])
+    led.admit(0, 5)   # 2 blocks
+    led.admit(1, 4)   # 1 block, sits on a boundary
+    assert led.free == 3 and led.blocks_next_step() == 1
+    led.advance()     # row 1 pops a block
+    assert led.free == 2 and led.seq_lens == {0: 6, 1: 5}
+    for _ in range(2):
+        led.advance()
+    assert led.seq_lens == {0: 8, 1: 7} and led.free == 2
+    led.advance()     # row 0 crosses into its third block
+    assert led.free == 1 and led.seq_lens == {0: 9, 1: 8}
+    led.advance()     # row 1 too
+    assert led.free == 0
+    for _ in range(3):
+        led.advance()
+    assert led.seq_lens == {0: 12, 1: 12}
+    led.advance()     # both tables full: nobody moves, nothing is popped
+    assert led.seq_lens == {0: 12, 1: 12} and led.free == 0
+    with pytest.raises(RuntimeError):
+        led.admit(0, 1)
+    led.release(0)
+    assert led.free == 3 and 0 not in led.seq_lens
+    # an empty list parks the row that needs a block, as the device does
+    led2 = BlockLedger(num_alloc_blocks=1, block_size=2, max_blocks_per_seq=4)
+    led2.admit(3, 2)
+    led2.advance()
+    assert led2.seq_lens[3] == 2 and led2.free == 0

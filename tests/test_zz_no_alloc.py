@@ -14,6 +14,7 @@ import torch
 
 import cases
 from conftest import to_dev
+from oracle import torch_oracle as orc
 from spikeinfer_b200 import _lib, kernels
 
 pytestmark = pytest.mark.gpu
@@ -45,6 +46,7 @@ def test_static_scratch_matches_workspace_path_twice_in_a_row(dev, lib):
         assert got.data_ptr() == out.data_ptr()
         assert torch.isfinite(got).all()
         assert rel_err(got, want) < REL_TOL
+        assert rel_err(got.cpu(), orc.paged_spike_attn_decode(**case)) < REL_TOL  # and against the CPU oracle itself
     # bf16 output into a strided view, as the engine passes it
     buf = torch.zeros(4, 5, 14, 64, dtype=torch.bfloat16, device=dev)
     kernels.paged_spike_attn_decode_noalloc(**d, out=buf[:, :3])
