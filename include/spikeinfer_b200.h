@@ -71,7 +71,9 @@ enum {
     SPK_STATUS_POOL_EXHAUSTED = 1u << 3,/* metadata builder ran out of free blocks          */
     SPK_STATUS_TABLE_FULL = 1u << 4,    /* a row needs more than max_blocks blocks          */
     SPK_STATUS_FREE_LIST_OVERFLOW = 1u << 5, /* a release would push past the list's capacity    */
-    SPK_STATUS_ROW_BUSY = 1u << 6       /* admit into a row that still holds a sequence      */
+    SPK_STATUS_ROW_BUSY = 1u << 6,      /* admit into a row that still holds a sequence      */
+    SPK_STATUS_DEVICE_WAIT_EXPIRED = 1u << 7 /* a kernel gave up waiting for its own tensor-core work;
+                                            the affected rows of the output are zero           */
 };
 
 /* Library version, (major << 16) | (minor << 8) | patch. */
@@ -230,6 +232,18 @@ int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int64_t sq_h,
                     int T, int64_t n_seqs, int num_q_heads, int num_kv_heads, int head_dim,
                     int block_size, int64_t max_blocks, int64_t num_blocks, float scale,
                     void* workspace, int64_t workspace_bytes, uint32_t* status, void* stream);
+
+/* Which form of the attention kernel spk_attn_decode takes (no counterpart in the reference; it lets tests and
+ * benchmarks run one form against another).  AUTO: the streaming mma.sync form where the layout allows it
+ * (pages of contiguous, 16-byte aligned rows, head_dim 64 or 128), else the general form.  GENERAL: always the
+ * general form.  TCGEN05: the tcgen05 / tensor-memory form where it applies (head_dim 64, BF16/F16 output, at most
+ * 1024 sequences, scale * head_dim <= 16), else as AUTO.  Process-wide; returns SPK_ERR_UNSUPPORTED for other values. */
+enum {
+    SPK_ATTN_FORM_AUTO = 0,
+    SPK_ATTN_FORM_GENERAL = 1,
+    SPK_ATTN_FORM_TCGEN05 = 2
+};
+int spk_attn_select_form(int form);
 
 /* spk_attn_decode for callers that cannot allocate (no counterpart in the reference).
  *

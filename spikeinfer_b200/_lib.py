@@ -24,8 +24,11 @@ STATUS_POOL_EXHAUSTED = 1 << 3
 STATUS_TABLE_FULL = 1 << 4
 STATUS_FREE_LIST_OVERFLOW = 1 << 5
 STATUS_ROW_BUSY = 1 << 6
+STATUS_DEVICE_WAIT_EXPIRED = 1 << 7
 
 MAX_LIF_SITES = 4
+
+ATTN_FORM_AUTO, ATTN_FORM_GENERAL, ATTN_FORM_TCGEN05 = 0, 1, 2
 
 _DTYPE_CODES = {
     torch.float32: F32,
@@ -128,6 +131,7 @@ SIGNATURES = {
     "spk_meta_advance": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p,
                                  c_void_p]),
+    "spk_attn_select_form": (c_int, [c_int]),
     "spk_meta_admit": (c_int, [c_int32, c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
                                c_int32, c_void_p, c_void_p]),

@@ -30,7 +30,6 @@
 #include "spk_attn.cuh"
 
 #include <atomic>
-#include <cstdlib>
 
 namespace {
 
@@ -623,15 +622,6 @@ extern "C" int64_t spk_attn_decode_workspace_bytes(int T, int64_t n_seqs, int nu
     return general > streaming ? general : streaming;
 }
 
-// SPK_ATTN_FORM=general in the environment keeps every call on the general form (for timing one against the other).
-static bool general_form_forced() {
-    static const bool forced = [] {
-        const char* e = std::getenv("SPK_ATTN_FORM");
-        return e != nullptr && e[0] == 'g';
-    }();
-    return forced;
-}
-
 extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int64_t sq_h,
                                const int32_t* k, int64_t sk_t, int64_t sk_h, int64_t sk_blk, int64_t sk_slot,
                                const int32_t* v, int64_t sv_t, int64_t sv_h, int64_t sv_blk, int64_t sv_slot,
@@ -684,7 +674,7 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
     cudaStream_t s = spk_stream(stream);
     // Pages of contiguous, 16-byte aligned rows at head_dim 64 / 128 take the streaming form.
     const StreamPlan spl = spk_attn_stream_plan(T, n_seqs, num_q_heads, num_kv_heads, head_dim, block_size, max_blocks);
-    if (spl.ok && !general_form_forced() && spk_attn_stream_layout_ok(p, head_dim)) {
+    if (spl.ok && spk_attn_selected_form() != SPK_ATTN_FORM_GENERAL && spk_attn_stream_layout_ok(p, head_dim)) {
         if (spl.ws_bytes > 0 && (workspace == nullptr || workspace_bytes < spl.ws_bytes)) return SPK_ERR_WORKSPACE_TOO_SMALL;
         p.passes = spl.passes;
         return spk_attn_stream_launch(p, spl, head_dim, s);

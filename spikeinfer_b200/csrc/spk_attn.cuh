@@ -24,16 +24,21 @@ struct AttnParams {
 // Query heads served per pass over K and V: the eight columns of the MMA tile.
 constexpr int kAttnHeads = 8;
 
-// How the streaming form cuts the batch: every sequence into units of `unit_keys` keys, one warp per
-// (unit, KV head, pass, timestep).
+// How the streaming form cuts the batch (see spk_attn_stream.cu).
 struct StreamPlan {
     bool ok;            // the shape is one the streaming form handles
-    int unit_keys;      // keys per unit (512, 1024 or 2048)
-    int max_units;      // units of the longest possible row
+    bool dense;         // range form: the warps of the grid share one list of 32-key steps in equal parts
+    bool cut;           // range form: some item may be cut between warps (records and a combine pass exist)
+    int64_t workers;    // range form: warps sharing the list
+    int unit_keys;      // unit form: keys per unit (512, 1024 or 2048)
+    int max_units;      // unit form: units of the longest possible row
     int passes;         // passes per KV head (eight query heads each)
     int64_t rec_floats; // floats per partial record: 8 * head_dim sums + 8 weight totals
-    int64_t ws_bytes;   // partial records of rows cut into several units (0 when max_units == 1)
+    int64_t ws_bytes;   // partial records (and, range form, the step prefix); 0 when nothing can be cut
 };
+
+// Form picked by spk_attn_select_form (SPK_ATTN_FORM_*).
+int spk_attn_selected_form();
 
 StreamPlan spk_attn_stream_plan(int T, int64_t n_seqs, int Hq, int Hkv, int head_dim, int block_size,
                                 int64_t max_blocks);

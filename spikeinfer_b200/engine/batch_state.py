@@ -109,5 +109,6 @@ class DecodeBatchState:
                                     ("bad slot", _lib.STATUS_BAD_SLOT), ("pool exhausted", _lib.STATUS_POOL_EXHAUSTED),
                                     ("block table full", _lib.STATUS_TABLE_FULL),
                                     ("free list overflow", _lib.STATUS_FREE_LIST_OVERFLOW),
-                                    ("row busy", _lib.STATUS_ROW_BUSY)) if bits & b]
+                                    ("row busy", _lib.STATUS_ROW_BUSY),
+                                    ("device wait expired", _lib.STATUS_DEVICE_WAIT_EXPIRED)) if bits & b]
             raise _lib.SpkError("device status: " + ", ".join(names))

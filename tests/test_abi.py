@@ -55,15 +55,15 @@ def test_host_side_argument_checks(lib):
     assert lib.spk_attn_decode(*args(48, 16)) == -6
     assert lib.spk_attn_decode(*args(64, 12)) == -6
     assert lib.spk_attn_decode(*args(256, 16)) == -6
-    # workspace = partial records of rows cut into 512-key units: none while a row cannot exceed one unit;
-    # 64 sequences of up to 4096 keys (the kernel-level attention configuration): 8 units per row, one record
-    # per (sequence, timestep, KV head, unit).
+    # workspace of the streaming form: two partial records per worker warp plus the step prefix, and only when a
+    # sequence can be long enough (more than 512 keys) to be cut between warps.  Workers: one per eight 32-key
+    # steps of the fully loaded batch, at most 148 SMs x 16 warps.
     record = (8 * 64 + 8) * 4                    # eight heads x 64 sums + 8 totals, fp32
     assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 1) == 0
     assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 32) == 0
-    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 256) == 64 * 4 * 2 * 8 * record
+    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 256) == 148 * 16 * 2 * record + 65 * 4
     ws = lib.spk_attn_decode_workspace_bytes(4, 8, 14, 2, 64, 16, 256)
-    assert ws > 0 and ws % (8 * 4 * 2 * record) == 0
+    assert ws == (8 * 4 * 2 * 128 // 8) * 2 * record + 9 * 4
     assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 48, 16, 256) == 0
     # workspace required but missing -> rejected on the host, nothing launched
     big = (1, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 1, 1, _lib.F32, 0, 0, 0,
