@@ -185,7 +185,7 @@ __device__ __forceinline__ void store_channels(TO* dst, const float* src, float 
 #define SPK_STREAM_MINB 5
 #endif
 
-constexpr int kShortSteps = 16;  // an item of at most this many 32-key steps is never cut between warps
+constexpr int kShortSteps = 8;   // an item of at most this many 32-key steps (256 keys) is never cut between warps
 
 template <int W>
 struct StreamSmem {
@@ -1069,7 +1069,7 @@ StreamPlan spk_attn_stream_plan(int T, int64_t n_seqs, int Hq, int Hkv, int head
     if (pl.dense) {
         const int64_t max_steps = (max_keys + 31) / 32;
         const int64_t all_steps = n_seqs * gt * max_steps;
-        const int64_t cap = 148LL * kWarps * stream_ctas_per_sm(head_dim, /*wide=*/true);  // the same for every output type
+        const int64_t cap = 148LL * kWarps * stream_ctas_per_sm(head_dim, /*wide=*/false);  // the most any output type uses
         int64_t workers = (all_steps + 7) / 8;
         workers = workers < 1 ? 1 : (workers > cap ? cap : workers);
         pl.workers = workers;
@@ -1154,12 +1154,14 @@ int spk_attn_stream_launch(const AttnParams& p, const StreamPlan& plan, int head
     int64_t ctas;
     bool combine;
     if (plan.dense) {
-        sp.workers = plan.workers;
+        // as many warps as this output type keeps resident, within what the plan's workspace allows
+        const int64_t resident = 148LL * kWarps * stream_ctas_per_sm(head_dim, wide);
+        sp.workers = plan.workers < resident ? plan.workers : resident;
         sp.dense_ws = p.ws;
         sp.prefix_out = plan.cut ? reinterpret_cast<int*>(reinterpret_cast<char*>(p.ws) +
                                                           ((plan.workers * 2 * plan.rec_floats * 4 + 15) / 16) * 16)
                                  : nullptr;
-        ctas = (plan.workers + kWarps - 1) / kWarps;
+        ctas = (sp.workers + kWarps - 1) / kWarps;
         combine = plan.cut;
     } else {
         // worst case of the enumeration: every row of max_units units (the surplus warps leave at once)
