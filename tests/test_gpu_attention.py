@@ -205,21 +205,103 @@ def test_config2_full_size(dev):
     assert torch.equal(kernels.qk_scores(**to_dev(sub, dev)).cpu(), orc.qk_scores(**sub))
 
 
+def test_general_form_still_serves_every_layout(dev, lib):
+    """With the streaming form switched off, the general form takes the same calls (it is what small pages, odd
+    strides and head_dim 32 / 96 use): the kernel-level attention configuration against the oracle."""
+    assert lib.spk_attn_select_form(_lib.ATTN_FORM_GENERAL) == 0
+    try:
+        case = config2_case(n=16)
+        got = kernels.paged_spike_attn_decode(**to_dev(case, dev)).cpu()
+        assert rel_err(got, orc.paged_spike_attn_decode(**case)) < REL_TOL
+    finally:
+        assert lib.spk_attn_select_form(_lib.ATTN_FORM_AUTO) == 0
+
+
 def attention_fp64(case):
     """The same softmax-weighted sum in float64 from the unpacked bits: the yardstick for rows so long that the
     fp32 oracle's own rounding (3.8e-5 at 32768 keys) is above the bar."""
     D, Hq, Hkv = case["head_dim"], case["num_q_heads"], case["num_kv_heads"]
     q = orc.unpack_spikes(case["q_packed"], D, torch.float64)  # [T, n, Hq, D]
+    T, n_seqs = q.shape[:2]
     out = torch.zeros(q.shape, dtype=torch.float64)
-    for n in range(q.shape[1]):
+    for n in range(n_seqs):
         length = int(case["seq_lens"][n])
         k = orc.gather_kv_unpacked(case["k_cache"], case["block_tables"][n], length, D, case["block_size"], torch.float64)
         v = orc.gather_kv_unpacked(case["v_cache"], case["block_tables"][n], length, D, case["block_size"], torch.float64)
-        k = k.repeat_interleave(Hq // Hkv, dim=1)  # [T, Hq, L, D]
-        v = v.repeat_interleave(Hq // Hkv, dim=1)
-        s = torch.einsum("thd,thld->thl", q[:, n], k) * D ** -0.5
-        out[:, n] = torch.einsum("thl,thld->thd", torch.softmax(s, -1), v)
+        qg = q[:, n].view(T, Hkv, Hq // Hkv, D)  # the query heads of a group share their K/V head
+        s = torch.einsum("tgrd,tgld->tgrl", qg, k) * D ** -0.5
+        out[:, n] = torch.einsum("tgrl,tgld->tgrd", torch.softmax(s, -1), v).reshape(T, Hq, D)
     return out
+
+
+def test_long_context_shard_shape(dev):
+    """The attention of one tensor-parallel shard of the 7B-shape long-context configuration: head_dim 128, 7 query
+    heads on 1 KV head, T = 4, a dozen rows with lengths log-uniform in [1k, 32k] plus one of 32768, 16-token pages.
+    Rows are cut between many warps and combined.  fp32 output against float64 < 2e-6; bf16 output within 1e-3."""
+    import math
+    g = cases.gen(55)
+    lo, hi = math.log(1024.0), math.log(32768.0)
+    lens = torch.exp(torch.rand(11, generator=g) * (hi - lo) + lo).long().clamp(1024, 32768).tolist() + [32768]
+    case = cases.attention_case(seq_lens=lens, density=0.15, seed=55, spare_blocks=0, max_blocks=2048,
+                                head_dim=128, num_q_heads=7, num_kv_heads=1)
+    d = to_dev(case, dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    got = kernels.paged_spike_attn_decode(**d, status=status).cpu().double()
+    want = attention_fp64(case)
+    err = ((got - want).abs().max() / want.abs().max()).item()
+    assert err < 2e-6, f"{err:.2e}"
+    got16 = kernels.paged_spike_attn_decode(**d, dtype=torch.bfloat16).cpu()
+    assert within_bf16_bar(got16, want.float())
+    assert status.item() == 0
+
+
+@pytest.fixture
+def tcgen05_form(lib):
+    """Routes eligible calls to the tcgen05 / tensor-memory form for the duration of a test."""
+    assert lib.spk_attn_select_form(_lib.ATTN_FORM_TCGEN05) == 0
+    yield
+    assert lib.spk_attn_select_form(_lib.ATTN_FORM_AUTO) == 0
+
+
+@pytest.mark.parametrize("name", ["single_token", "ragged", "bs64", "gqa_4_2", "gqa_28_2", "T1", "T8", "long_split", "wide_table"])
+def test_tcgen05_form_matches_oracle(name, dev, tcgen05_form):
+    """The tcgen05 form (int8 MMAs out of shared memory, int32 sums in tensor memory) on the cases it applies to
+    (head_dim 64, 16-bit output): within the 16-bit bar of the oracle, status clean (no expired wait)."""
+    case = cases.attention_case(**cases.ATTENTION_CASES[name])
+    want = orc.paged_spike_attn_decode(**case)
+    for dtype in (torch.bfloat16, torch.float16):
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        got = run(case, dev, dtype=dtype, status=status).cpu()
+        assert torch.isfinite(got).all()
+        if dtype == torch.bfloat16:
+            assert within_bf16_bar(got, want)
+        else:
+            assert rel_err(got, want) < 1e-3
+        assert status.item() == 0
+
+
+def test_tcgen05_form_config2_and_linearity(dev, tcgen05_form):
+    """The kernel-level attention configuration through the tcgen05 form, plus linearity in V: the sums are exact
+    integers there, so out(V1 | V2) = out(V1) + out(V2) holds to the rounding of the 16-bit outputs."""
+    case = config2_case()
+    d = to_dev(case, dev)
+    want = orc.paged_spike_attn_decode(**case)
+    got = kernels.paged_spike_attn_decode(**d, dtype=torch.bfloat16).cpu()
+    assert within_bf16_bar(got, want)
+    mask = torch.tensor([0x0F0F0F0F, 0x33333333], dtype=torch.int32, device=dev)
+    d1, d2 = dict(d), dict(d)
+    d1["v_cache"] = d["v_cache"] & mask
+    d2["v_cache"] = d["v_cache"] & ~mask
+    o1 = kernels.paged_spike_attn_decode(**d1, dtype=torch.float16).float()
+    o2 = kernels.paged_spike_attn_decode(**d2, dtype=torch.float16).float()
+    o = kernels.paged_spike_attn_decode(**d, dtype=torch.float16).float()
+    torch.testing.assert_close(o1 + o2, o, rtol=0, atol=3 * 2.0 ** -11 * float(o.abs().max()))
+
+
+def test_form_selector_rejects_unknown_values(lib):
+    assert lib.spk_attn_select_form(7) == -6 and lib.spk_attn_select_form(-1) == -6
+    assert lib.spk_attn_select_form(_lib.ATTN_FORM_GENERAL) == 0
+    assert lib.spk_attn_select_form(_lib.ATTN_FORM_AUTO) == 0
 
 
 @pytest.mark.parametrize("seq_lens,max_blocks,density", [([32768], 2048, 0.2), ([9000, 2500], 1024, 0.5)])

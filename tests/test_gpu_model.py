@@ -93,6 +93,53 @@ def test_per_layer_operators_bit_exact_on_oracle_tensors(variant, dev, golden):
             assert torch.equal(prod.cpu(), c["gate_spk"] * up + 0.0), f"{step} layer {i}: gated product differs"
 
 
+def test_0p5b_shape_layer_bf16_teacher_forced(dev):
+    """One layer at the 0.5B shape (hidden 896, 14/2 heads, head_dim 64, MLP 4864, T = 4) in bf16, 64 decode rows:
+    the oracle's currents go into the fused launches, which must reproduce its spikes, packed q and K/V pools bit
+    for bit; the attention context (bf16) agrees within 1e-3; the gated MLP product is exact."""
+    shape = mo.ModelShape(vocab_size=2048, hidden_size=896, intermediate_size=4864, num_hidden_layers=1,
+                          num_attention_heads=14, num_key_value_heads=2, head_dim=64)
+    w = mo.init_weights(shape, seed=0, dtype=torch.bfloat16)
+    mo.randomize_lif(w, seed=1)
+    n, plen, bs = 64, 40, 16
+    run = mo.PagedRun(w, shape, num_blocks=n * 4 + 1, block_size=bs, max_model_len=64)
+    prompts = torch.randint(0, shape.vocab_size, (n, plen), generator=cases.gen(4)).tolist()
+    run.prefill(prompts)
+    k_before, v_before = run.k[0].clone(), run.v[0].clone()
+    cap: dict = {}
+    computed = list(run.computed)
+    run.decode(capture=cap)
+    c = cap[0]
+    hq, hkv, d, T = 14, 2, 64, 4
+    _, slots, bt, lens = orc.prepare_decode(run.tables, computed, run.max_blocks, run.pad_block, bs)
+    meta = AttentionMetadata(slot_mapping=slots.to(dev), block_size=bs, num_decode_tokens=n,
+                             block_tables=bt.to(dev), seq_lens=lens.to(dev))
+    assert c["q_cur"].dtype == torch.bfloat16
+    qkv = torch.cat([c[f"{x}_cur"].permute(0, 2, 1, 3).reshape(T, n, -1) for x in ("q", "k", "v")], dim=-1)
+    p = "model.layers.0.self_attn."
+    lif = [(w[p + f"lif_{x}.lif.beta"].to(dev), w[p + f"lif_{x}.lif.threshold"].to(dev)) for x in ("q", "k", "v")]
+    kc, vc = k_before.to(dev), v_before.to(dev)
+    ctx = fused_qkv_attention(qkv.to(dev), *lif, kc, vc, meta, hq, hkv, d)
+    assert torch.equal(kc.cpu(), run.k[0]) and torch.equal(vc.cpu(), run.v[0]), "K/V pools differ from the oracle's"
+    assert 0.02 < orc.unpack_spikes(run.k[0][:, :, : n * plen], d).mean() < 0.9, "spiking too sparse to be a check"
+    # fused rotary embedding: un-rotated currents in, identical pools and context out
+    pre = torch.cat([c[x].permute(0, 2, 1, 3).reshape(T, n, -1) for x in ("q_pre", "k_pre", "v_cur")], dim=-1)
+    kc2, vc2 = k_before.to(dev), v_before.to(dev)
+    ctx2 = fused_qkv_attention(pre.to(dev), *lif, kc2, vc2, meta, hq, hkv, d, rope=(c["cos"].to(dev), c["sin"].to(dev)))
+    assert torch.equal(kc2, kc) and torch.equal(vc2, vc) and torch.equal(ctx2, ctx)
+    assert ctx.dtype == torch.bfloat16
+    want = c["ctx"].float()
+    scale = want.abs().max().clamp(min=1e-6)
+    # both sides round to bf16 after an fp32 evaluation: 1e-3 of the largest value plus a bf16 step of the value
+    assert ((ctx.cpu().float() - want).abs() <= 1e-3 * scale + want.abs() * 2.0 ** -7).all()
+    pg = "model.layers.0.mlp.lif_gate.lif."
+    gate = kernels.lif_multistep(c["gate_cur"].to(dev), w[pg + "beta"].to(dev), w[pg + "threshold"].to(dev))
+    assert torch.equal(gate.cpu(), c["gate_spk"])
+    up = torch.randn(c["gate_cur"].shape, generator=cases.gen(9)).to(torch.bfloat16)
+    prod = kernels.lif_gate_mul(c["gate_cur"].to(dev), up.to(dev), w[pg + "beta"].to(dev), w[pg + "threshold"].to(dev))
+    assert torch.equal(prod.cpu(), c["gate_spk"] * up + 0.0)
+
+
 @pytest.mark.parametrize("packed_prefill", [True, False])
 @pytest.mark.parametrize("use_graph", [False, True])
 @pytest.mark.parametrize("variant", ["constant_lif", "random_lif"])

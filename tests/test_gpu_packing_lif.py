@@ -216,19 +216,22 @@ def test_fused_bad_slot_is_skipped_and_flagged(dev):
     assert (pool[:, 0, 3] == -1).all()
 
 
-def test_config3_full_size_gate_and_kv(dev):
-    """BASELINE config 3 at full size: gate [4, 8192, 4864] bf16 and k/v [4, 8192, 2x64] scattered through a
-    random slot permutation of a 16-token-page pool.  Packed bits, membrane and pool bit-exact vs the oracle."""
+@pytest.mark.parametrize("reset_mode", [orc.SUBTRACT_DELAYED, orc.HARD_ZERO], ids=["subtract_delayed", "hard_zero"])
+def test_config3_full_size_gate_and_kv(reset_mode, dev):
+    """The fused LIF + bit-pack + paged K/V write at full size: gate [4, 8192, 4864] bf16 and k/v [4, 8192, 2x64]
+    scattered through a random slot permutation of a 16-token-page pool.  Packed bits, membrane and pool bit-exact
+    vs the oracle, in both reset rules.  SUBTRACT_DELAYED is the reference's rule (pinned by its own restatement);
+    HARD_ZERO exists only here: parity unpinned, the comparison is against this project's own CPU definition."""
     T, n_tok, N, Hkv, D, bs = 4, 8192, 4864, 2, 64, 16
     g = cases.gen(3)
     th = torch.rand(N, generator=g) + 0.5
     beta = torch.full((N,), 0.9)
     chunk = 1024  # the oracle works through the tokens in chunks to bound host memory
     gate = torch.randn(T, n_tok, N, generator=g).to(torch.bfloat16)
-    packed, _, mem = kernels.lif_pack(gate.to(dev), beta.to(dev), th.to(dev), return_membrane=True)
+    packed, _, mem = kernels.lif_pack(gate.to(dev), beta.to(dev), th.to(dev), return_membrane=True, reset_mode=reset_mode)
     packed, mem = packed.cpu(), mem.cpu()
     for s in range(0, n_tok, chunk):
-        ws, wu = orc.lif_multistep(gate[:, s:s + chunk], beta, th, out_dtype=torch.uint8)
+        ws, wu = orc.lif_multistep(gate[:, s:s + chunk], beta, th, out_dtype=torch.uint8, reset_mode=reset_mode)
         assert torch.equal(packed[:, s:s + chunk], orc.pack_spikes(ws))
         assert torch.equal(mem[s:s + chunk], wu)
     rate = orc.unpack_spikes(packed[:, :256], N).mean().item()
@@ -245,9 +248,10 @@ def test_config3_full_size_gate_and_kv(dev):
                            packed_strides=(pool.stride(0), pool.stride(2), pool.stride(1)),
                            slot_mapping=slots.to(dev), num_rows=n_tok)
     kernels.lif_pack_scatter([mk(d[..., : Hkv * D].view(T, n_tok, Hkv, D), k_pool),
-                              mk(d[..., Hkv * D:].view(T, n_tok, Hkv, D), v_pool)])
+                              mk(d[..., Hkv * D:].view(T, n_tok, Hkv, D), v_pool)], reset_mode=reset_mode)
     for x, pool in ((kv[..., : Hkv * D], k_pool), (kv[..., Hkv * D:], v_pool)):
-        s, _ = orc.lif_multistep(x.view(T, n_tok, Hkv, D), torch.full((D,), 0.9), th_kv, out_dtype=torch.uint8)
+        s, _ = orc.lif_multistep(x.view(T, n_tok, Hkv, D), torch.full((D,), 0.9), th_kv, out_dtype=torch.uint8,
+                                 reset_mode=reset_mode)
         want = torch.zeros(T, Hkv, n_tok, 2, dtype=torch.int32).index_copy_(
             2, slots, orc.pack_spikes(s).permute(0, 2, 1, 3).contiguous())
         assert torch.equal(pool.cpu(), want)
