@@ -1,7 +1,7 @@
 """Generate tests/golden/*.pt by running the reference's own CPU code on the seeded cases.
 
-Run once in a container that has the reference checkout (default /root/reference):
-    python tests/golden/make_golden.py [/path/to/reference]
+Run once in a container that has the reference checkout:
+    python tests/golden/make_golden.py /path/to/reference
 
 The reference package's ``__init__`` pulls in snntorch (absent here), so the kernel modules are
 imported through empty parent-package objects that only carry ``__path__``; the modules used
@@ -10,7 +10,10 @@ reference's OUTPUTS (plus a digest of the seeded inputs); no reference source is
 """
 from __future__ import annotations
 
+import dataclasses
 import importlib
+import inspect
+import json
 import sys
 import types
 from pathlib import Path
@@ -38,10 +41,40 @@ def import_reference(ref_root: str):
     return kernels, cpu, bm
 
 
+def describe_callable(fn) -> list[dict]:
+    """Parameters of ``fn`` as plain data: name, kind, whether it has a default and the default's repr."""
+    out = []
+    for prm in inspect.signature(fn).parameters.values():
+        has_default = prm.default is not inspect.Parameter.empty
+        out.append(dict(name=prm.name, kind=prm.kind.name, has_default=has_default,
+                        default=repr(prm.default) if has_default else None))
+    return out
+
+
+def record_interface(kernels, ref_root: str) -> None:
+    """The operator surface a drop-in has to keep: every export of the reference's ``kernels`` package with its
+    signature, ``paged_attention`` and the fields of ``AttentionMetadata``.  Written as JSON next to the fixtures."""
+    surface = {}
+    for name in kernels.__all__:
+        obj = getattr(kernels, name)
+        surface[name] = dict(params=describe_callable(obj)) if callable(obj) else dict(value=obj)
+    attention = importlib.import_module("spikeinfer.attention")
+    surface["paged_attention"] = dict(params=describe_callable(attention.paged_attention))
+    fields = []
+    for f in dataclasses.fields(attention.AttentionMetadata):
+        has_default = f.default is not dataclasses.MISSING or f.default_factory is not dataclasses.MISSING
+        fields.append(dict(name=f.name, has_default=has_default, public=not f.name.startswith("_")))
+    surface["AttentionMetadata"] = dict(fields=fields)
+    (HERE / "interface.json").write_text(json.dumps(surface, indent=1, sort_keys=True) + "\n")
+
+
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference")
+    ref_root = sys.argv[1]
     kernels, cpu, bm = import_reference(ref_root)
     torch.set_num_threads(4)
+    record_interface(kernels, ref_root)
 
     # ---- packing -----------------------------------------------------------
     pack = {}

@@ -2,7 +2,7 @@
 configuration (4 layers, hidden 256, 4/2 heads, head_dim 64, MLP 1024, vocab 32000, T=4, page 16,
 4 prompts x 32 random ids, 16 greedy tokens) on CPU in fp32.
 
-Run once where the reference checkout exists:  python tests/golden/make_golden_engine.py [/root/reference]
+Run once where the reference checkout exists:  python tests/golden/make_golden_engine.py /path/to/reference
 
 The reference imports snntorch only to hold the LIF parameters (its neuron is never stepped on the
 engine path: spikeinfer/modeling_fast.py:32-34), so a stand-in module that registers ``beta`` /
@@ -134,7 +134,9 @@ def run_reference(ref_root: str, randomize: bool):
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden_engine.py /path/to/reference")
+    ref_root = sys.argv[1]
     with tempfile.TemporaryDirectory() as tmp:
         pkg = Path(tmp) / "snntorch"
         pkg.mkdir()

@@ -3,6 +3,9 @@ Host-side argument validation is exercised too; none of these calls launches a k
 from __future__ import annotations
 
 import ctypes
+import dataclasses
+import inspect
+import json
 import re
 from pathlib import Path
 
@@ -82,3 +85,51 @@ def test_host_side_argument_checks(lib):
     assert lib.spk_argmax(None, _lib.F32, 4, 16, 16, 1, 1, 1 << 20, None) == -4     # null logits
     assert lib.spk_argmax(1, _lib.F32, 4, 16, 16, 1, None, 0, None) == -5           # workspace missing
     assert lib.spk_argmax(1, _lib.F32, 70000, 16, 16, 1, 1, 1 << 30, None) == -7    # more rows than a grid dimension
+
+
+def _params(fn):
+    out = []
+    for prm in inspect.signature(fn).parameters.values():
+        has_default = prm.default is not inspect.Parameter.empty
+        out.append(dict(name=prm.name, kind=prm.kind.name, has_default=has_default,
+                        default=repr(prm.default) if has_default else None))
+    return out
+
+
+def test_operator_surface_matches_the_reference():
+    """Drop-in conformance: every operator the reference's ``kernels`` package exports for this path exists here
+    under the same name with the same leading parameters (name, order, kind, default); extra parameters are
+    allowed only at the end and only with defaults.  ``AttentionMetadata`` keeps every public field, in order.
+    The recorded surface comes from the reference itself (tests/golden/make_golden.py)."""
+    from spikeinfer_b200 import attention, kernels
+
+    surface = json.loads((Path(__file__).parent / "golden" / "interface.json").read_text())
+    # the reference's own CPU restatements are its test oracles, not operators of the path: there is no CPU path here
+    not_provided = {"lif_multistep_ref", "paged_spike_attn_decode_ref", "paged_spike_attn_decode_cpu"}
+    checked = 0
+    for name, entry in surface.items():
+        if name in not_provided or name == "AttentionMetadata":
+            continue
+        where = attention if name == "paged_attention" else kernels
+        assert hasattr(where, name), f"{name} is missing"
+        mine = getattr(where, name)
+        if "value" in entry:
+            assert mine == entry["value"], name
+            continue
+        got, want = _params(mine), entry["params"]
+        assert got[: len(want)] == want, f"{name}: {got[:len(want)]} != {want}"
+        for extra in got[len(want):]:
+            assert extra["has_default"], f"{name}: extra parameter {extra['name']} needs a default"
+        checked += 1
+    assert checked >= 8
+    assert not_provided <= set(surface), "the reference's export list changed"
+    mine = [f.name for f in dataclasses.fields(attention.AttentionMetadata)]
+    theirs = [f["name"] for f in surface["AttentionMetadata"]["fields"] if f["public"]]
+    assert mine[: len(theirs)] == theirs
+    defaults = {f.name: (f.default is not dataclasses.MISSING or f.default_factory is not dataclasses.MISSING)
+                for f in dataclasses.fields(attention.AttentionMetadata)}
+    for f in surface["AttentionMetadata"]["fields"]:
+        if f["public"]:
+            assert defaults[f["name"]] == f["has_default"], f["name"]
+    for extra in mine[len(theirs):]:
+        assert defaults[extra], f"extra metadata field {extra} needs a default"
