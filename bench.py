@@ -8,13 +8,19 @@ thresholds calibrated to ~15 % q/k/v and ~5 % gate firing), 64 concurrent reques
 128-token random prompts, greedy decode, page size 16.  One step = one decode step of all 64 requests
 (64 tokens) as a single CUDA-graph replay: on-GPU metadata advance, 24 layers, lm_head, argmax.
 
-  value   decode tok/s with tokens looping on the device (inputs resident in HBM).
+  value   decode tok/s with tokens looping on the device (inputs resident in HBM), the first K timed steps.
+  spread  the same K steps repeated from the same batch state: median / min / max of every timed quantity.
   e2e     the same steps through ``SpikeDecodeEngine.step_host``: every step copies the input tokens
           from pinned host memory and reads the sampled tokens back.
-  roofline  paged popcount attention kernel at the kernel-level configuration the metric names
-          (64 ragged sequences in [128, 4096], 14/2 heads, D 64, T 4, Bernoulli(0.2) bits, 16-token
-          pages, bf16 out), timed with CUDA events over 24 distinct pools back to back (430 MB of K/V,
-          larger than L2); achieved = algorithmic bytes / launch time against the measured HBM copy peak.
+  roofline  paged popcount attention at the kernel-level configuration the metric names (64 ragged sequences in
+          [128, 4096], 14/2 heads, D 64, T 4, Bernoulli(0.2) bits, 16-token pages, bf16 out), timed with CUDA
+          events over 24 distinct pools back to back (430 MB of K/V, larger than L2); achieved = algorithmic
+          bytes / time per call against the measured HBM copy peak.  ``other_shapes``: the same for larger batches.
+  roofline_lif  fused LIF + bit-pack (+ paged K/V write) at its kernel-level configuration, both reset rules.
+  closed_loop  the reference's own serving protocol (spikeinfer/bench.py:29-116: N requests, C in flight, 128 in /
+          64 out): prefill, admission, release and the host visits inside the clock; output tok/s, TTFT, ITL.
+  open_loop  the same requests arriving as a Poisson process at 8 req/s (arrival-bound by construction).
+  strong_scaling  64 requests in total over the N GPUs of the run (the headline is 64 per GPU).
   cpu_baseline  the CPU oracle port of the reference's paged model path, timed on this host's cores on
           a bounded sample of the same workload.
 
@@ -50,6 +56,25 @@ N_REQ = 64
 PROMPT_LEN = 128
 BLOCK_SIZE = 16
 FALLBACK_HBM_GBS = 6650.0
+
+
+def stats(values: list[float], digits: int = 4) -> dict:
+    return {"median": round(statistics.median(values), digits), "min": round(min(values), digits),
+            "max": round(max(values), digits), "repeats": len(values)}
+
+
+def measured_traffic(key: str):
+    """DRAM bytes per launch of a kernel at a named workload, from the ncu capture summarised in
+    profiles/dram_traffic.txt (lines ``key bytes``).  None when the kernel has no capture under that key, so a
+    kernel that changed its name or shape without a new capture reports no traffic instead of a stale figure."""
+    try:
+        for line in (ROOT / "profiles" / "dram_traffic.txt").read_text().splitlines():
+            parts = line.split()
+            if len(parts) >= 2 and not line.startswith("#") and parts[0] == key:
+                return float(parts[1])
+    except OSError:
+        pass
+    return None
 
 
 def hbm_peak():
@@ -160,57 +185,192 @@ def total_decode_steps(K: int, W: int) -> int:
     return 2 * (K + W) + 8  # device-timed and host-in-the-loop passes, plus slack
 
 
-def build_engine(device, seed: int, total_steps: int, rank: int = 0, world: int = 1):
-    """0.5B-shape model, calibrated thresholds, 64 requests prefilled, decode graph captured."""
-    from spikeinfer_b200 import _lib
+def build_model(device, seed: int):
+    """0.5B-shape model with thresholds calibrated on 8 seeded prompts."""
     from spikeinfer_b200.calibrate import calibrate_thresholds
-    from spikeinfer_b200.engine.decode_engine import SpikeDecodeEngine
     from spikeinfer_b200.modeling import SpikingQwenConfig, SpikingQwenModel
 
     cfg = SpikingQwenConfig.qwen2_5_0p5b()
     weights = random_weights_device(cfg, device, torch.bfloat16, seed)
     model = SpikingQwenModel(cfg, weights, device=device)
     del weights
-    from spikeinfer_b200.engine.replicas import shard_requests
-
-    g = torch.Generator(device="cpu").manual_seed(seed + 1)
-    all_prompts = torch.randint(0, cfg.vocab_size, (N_REQ * world, PROMPT_LEN), generator=g)
-    mine = shard_requests(N_REQ * world, world, rank)  # this replica's share of the job's requests
-    prompts = all_prompts[mine.start:mine.stop]
-    rates = calibrate_thresholds(model, prompts[:8].to(device))
+    g = torch.Generator(device="cpu").manual_seed(seed + 7)
+    calib = torch.randint(0, cfg.vocab_size, (8, PROMPT_LEN), generator=g)
+    rates = calibrate_thresholds(model, calib.to(device))
     model.validate_thresholds()
-    max_len = model_len(total_steps)
+    return cfg, model, rates
+
+
+def build_engine(model, prompts: torch.Tensor, max_len: int, device):
+    """Engine with one decode row per prompt: prompts prefilled in groups of 16, decode graph captured.
+    Returns (engine, launches of this library per decode step)."""
+    from spikeinfer_b200 import _lib
+    from spikeinfer_b200.engine.decode_engine import SpikeDecodeEngine
+
+    n = prompts.shape[0]
     blocks_per_seq = -(-max_len // BLOCK_SIZE)
-    engine = SpikeDecodeEngine(model, num_blocks=N_REQ * blocks_per_seq + 1, block_size=BLOCK_SIZE,
-                               max_num_seqs=N_REQ, max_model_len=max_len)
-    for s in range(0, N_REQ, 16):  # prefill in groups of 16 prompts
+    engine = SpikeDecodeEngine(model, num_blocks=n * blocks_per_seq + 1, block_size=BLOCK_SIZE,
+                               max_num_seqs=n, max_model_len=max_len)
+    for s in range(0, n, 16):
         engine.add_requests(prompts[s:s + 16].tolist())
     lib = _lib.load()
     before = lib.spk_launch_count()
     engine.capture()
-    captured = lib.spk_launch_count() - before
-    launches_per_step = captured // 4  # three warm-up passes and the captured one
+    launches_per_step = (lib.spk_launch_count() - before) // 4  # three warm-up passes and the captured one
     torch.cuda.synchronize(device)
     engine.state.check_status()
-    return engine, rates, launches_per_step, max_len
+    return engine, launches_per_step
+
+
+def job_prompts(cfg, seed: int, n_total: int) -> torch.Tensor:
+    g = torch.Generator(device="cpu").manual_seed(seed + 1)
+    return torch.randint(0, cfg.vocab_size, (n_total, PROMPT_LEN), generator=g)
+
+
+# --------------------------------------------------------------------------- serving protocols (secondary keys)
+OUT_LEN = 64
+
+
+def percentile(values: list[float], q: float) -> float:
+    v = sorted(values)
+    return v[min(len(v) - 1, int(q * len(v)))]
+
+
+def closed_loop(model, cfg, device, concurrency: int, n_requests: int, k: int = 9, packed_prefill: bool = False,
+                seed: int = 77) -> dict:
+    """The reference's closed-loop protocol (spikeinfer/bench.py:29-116): `concurrency` requests in flight, each
+    replaced by the next one as soon as it finishes, 128 prompt tokens in, 64 greedy tokens out.  Everything is
+    inside the clock: prefill (groups of up to 16 prompts), admission, the host visit that reads the tokens (one
+    per k decode steps; the reference visits every step), release.  The decode graph is captured for exactly
+    `concurrency` rows (the reference keeps one graph per batch-size bucket)."""
+    from spikeinfer_b200.engine.decode_engine import SpikeDecodeEngine
+
+    max_len = -(-(PROMPT_LEN + OUT_LEN + BLOCK_SIZE) // BLOCK_SIZE) * BLOCK_SIZE
+    engine = SpikeDecodeEngine(model, num_blocks=concurrency * (max_len // BLOCK_SIZE) + 1, block_size=BLOCK_SIZE,
+                               max_num_seqs=concurrency, max_model_len=max_len, packed_prefill=packed_prefill)
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    prompts = torch.randint(0, cfg.vocab_size, (n_requests + 2, PROMPT_LEN), generator=g).tolist()
+    sync = lambda: torch.cuda.synchronize(device)
+    # warm-up, as the reference does (two requests): prefill kernels, graph capture
+    rows = engine.add_requests(prompts[-2:][:min(2, concurrency)])
+    engine.capture()
+    engine.decode_steps(2)
+    for r in rows:
+        engine.release(r)
+    sync()
+
+    pending = list(range(n_requests))
+    inflight: dict[int, list] = {}  # row -> [request, tokens produced, submit time, first-token time]
+    ttft, itl, visits = [], [], 0
+    t0 = time.perf_counter()
+    freed_at = t0
+    while pending or inflight:
+        while pending and engine.free_rows:
+            group = [pending.pop(0) for _ in range(min(16, len(pending), len(engine.free_rows)))]
+            rows = engine.add_requests([prompts[i] for i in group])
+            sync()
+            now = time.perf_counter()
+            for i, r in zip(group, rows):
+                inflight[r] = [i, 1, freed_at, now]
+                ttft.append(now - freed_at)
+        steps = min(k, min(OUT_LEN - v[1] for v in inflight.values()))
+        engine.decode_steps(steps)  # one host visit
+        visits += 1
+        now = time.perf_counter()
+        for r in list(inflight):
+            inflight[r][1] += steps
+            if inflight[r][1] >= OUT_LEN:
+                itl.append((now - inflight[r][3]) / (OUT_LEN - 1))
+                engine.release(r)
+                del inflight[r]
+                freed_at = now
+    sync()
+    wall = time.perf_counter() - t0
+    engine.state.check_status()
+    return {"concurrency": concurrency, "requests": n_requests, "output_tok_per_s": round(n_requests * OUT_LEN / wall, 1),
+            "ttft_ms_p50": round(percentile(ttft, 0.5) * 1e3, 2), "ttft_ms_p99": round(percentile(ttft, 0.99) * 1e3, 2),
+            "itl_ms_mean": round(statistics.mean(itl) * 1e3, 4), "wall_s": round(wall, 3),
+            "decode_steps_per_host_visit": k, "host_visits": visits,
+            "prefill": "batched popcount kernel over the packed pool" if packed_prefill
+                       else "per-sequence SDPA on unpacked spikes (the reference's arithmetic)"}
+
+
+def open_loop(model, cfg, device, rate: float = 8.0, n_requests: int = 64, seed: int = 78) -> dict:
+    """64 requests arriving as a Poisson process at `rate` per second, 128 in / 64 out, up to 64 rows.  The offered
+    load is rate x 64 = 512 output tok/s, far below what one GPU decodes, so the run is ARRIVAL-BOUND: its
+    throughput says nothing about the GPU; TTFT and inter-token latency do.  One host visit per decode step."""
+    from spikeinfer_b200.engine.decode_engine import SpikeDecodeEngine
+
+    max_len = -(-(PROMPT_LEN + OUT_LEN + BLOCK_SIZE) // BLOCK_SIZE) * BLOCK_SIZE
+    engine = SpikeDecodeEngine(model, num_blocks=N_REQ * (max_len // BLOCK_SIZE) + 1, block_size=BLOCK_SIZE,
+                               max_num_seqs=N_REQ, max_model_len=max_len)
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    prompts = torch.randint(0, cfg.vocab_size, (n_requests + 1, PROMPT_LEN), generator=g).tolist()
+    arrivals = torch.cumsum(torch.empty(n_requests).exponential_(rate, generator=g), 0).tolist()
+    sync = lambda: torch.cuda.synchronize(device)
+    rows = engine.add_requests(prompts[-1:])
+    engine.capture()
+    engine.decode_steps(2)
+    engine.release(rows[0])
+    sync()
+
+    inflight: dict[int, list] = {}
+    ttft, itl, nxt, done, busy_steps = [], [], 0, 0, 0
+    t0 = time.perf_counter()
+    while done < n_requests:
+        now = time.perf_counter() - t0
+        group = []
+        while nxt < n_requests and arrivals[nxt] <= now and len(group) < len(engine.free_rows):
+            group.append(nxt)
+            nxt += 1
+        if group:
+            rows = engine.add_requests([prompts[i] for i in group])
+            sync()
+            now = time.perf_counter() - t0
+            for i, r in zip(group, rows):
+                inflight[r] = [i, 1, arrivals[i], now]
+                ttft.append(now - arrivals[i])
+        if inflight:
+            engine.decode_steps(1)
+            busy_steps += 1
+            now = time.perf_counter() - t0
+            for r in list(inflight):
+                inflight[r][1] += 1
+                if inflight[r][1] >= OUT_LEN:
+                    itl.append((now - inflight[r][3]) / (OUT_LEN - 1))
+                    engine.release(r)
+                    del inflight[r]
+                    done += 1
+        elif nxt < n_requests:
+            time.sleep(max(0.0, arrivals[nxt] - (time.perf_counter() - t0)))
+    wall = time.perf_counter() - t0
+    engine.state.check_status()
+    return {"arrival_rate_req_per_s": rate, "requests": n_requests, "offered_output_tok_per_s": rate * OUT_LEN,
+            "output_tok_per_s": round(n_requests * OUT_LEN / wall, 1), "arrival_bound": True,
+            "ttft_ms_p50": round(percentile(ttft, 0.5) * 1e3, 2), "ttft_ms_p99": round(percentile(ttft, 0.99) * 1e3, 2),
+            "itl_ms_mean": round(statistics.mean(itl) * 1e3, 4), "wall_s": round(wall, 2), "decode_steps": busy_steps}
 
 
 # --------------------------------------------------------------------------- attention roofline (kernel level)
-def attention_roofline(device, n_pools: int = 24, iters: int = 10) -> dict:
+ATTN_KERNEL = "attn_stream_kernel<W=2,NB=1,dense>"  # what bf16 output at head_dim 64 launches (+ its combine pass)
+
+
+def time_attention(device, lens, max_blocks, n_pools, iters, repeats, hd=64, hq=14, hkv=2) -> dict:
+    """One call = the main kernel plus its combine pass over one pool; `n_pools` distinct pools back to back inside
+    one CUDA graph (their K/V together exceed L2), `iters` replays per timed region, `repeats` regions."""
     import cases
     from spikeinfer_b200 import kernels
 
-    g = cases.gen(2)
-    lens = torch.randint(128, 4097, (N_REQ,), generator=g).tolist()
-    case = cases.attention_case(seq_lens=lens, density=0.2, seed=2, spare_blocks=0, max_blocks=4096 // BLOCK_SIZE)
+    case = cases.attention_case(seq_lens=lens, density=0.2, seed=2, spare_blocks=0, max_blocks=max_blocks,
+                                head_dim=hd, num_q_heads=hq, num_kv_heads=hkv)
     d = {k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
     pools = [(d["k_cache"].clone(), d["v_cache"].clone()) for _ in range(n_pools)]
-    out = torch.empty(4, N_REQ, 14, 64, dtype=torch.bfloat16, device=device)
+    out = torch.empty(4, len(lens), hq, hd, dtype=torch.bfloat16, device=device)
 
     def run_all():
         for k, v in pools:
-            kernels.paged_spike_attn_decode(d["q_packed"], k, v, d["block_tables"], d["seq_lens"], 64, BLOCK_SIZE,
-                                            14, 2, out=out)
+            kernels.paged_spike_attn_decode(d["q_packed"], k, v, d["block_tables"], d["seq_lens"], hd, BLOCK_SIZE,
+                                            hq, hkv, out=out)
 
     run_all()
     torch.cuda.synchronize(device)
@@ -220,35 +380,61 @@ def attention_roofline(device, n_pools: int = 24, iters: int = 10) -> dict:
     for _ in range(3):
         graph.replay()
     torch.cuda.synchronize(device)
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(iters):
-        graph.replay()
-    stop.record()
-    torch.cuda.synchronize(device)
-    us = start.elapsed_time(stop) * 1e3 / (iters * n_pools)
-    sum_len = sum(lens)
+    us = []
+    for _ in range(repeats):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(iters):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize(device)
+        us.append(start.elapsed_time(stop) * 1e3 / (iters * n_pools))
+    W = hd // 32
+    n = len(lens)
     # algorithmic bytes of one call: K+V once per KV head, q, bf16 out, block-table entries, lengths
-    alg = sum_len * 4 * 2 * 2 * 2 * 4 + 4 * N_REQ * 14 * 2 * 4 + 4 * N_REQ * 14 * 64 * 2 \
-        + sum(-(-l // BLOCK_SIZE) for l in lens) * 4 + N_REQ * 4
+    alg = sum(lens) * 4 * hkv * 2 * W * 4 + 4 * n * hq * W * 4 + 4 * n * hq * hd * 2 \
+        + sum(-(-l // BLOCK_SIZE) for l in lens) * 4 + n * 4
+    peak, _ = hbm_peak()
+    med = statistics.median(us)
+    return {"us_per_call": stats(us, 2), "algorithmic_bytes": alg, "achieved_GBs": round(alg / med / 1e3, 1),
+            "frac": round(alg / med / 1e3 / peak, 4), "pools": n_pools, "sum_keys": sum(lens)}
+
+
+def attention_roofline(device, n_pools: int = 24, iters: int = 10, repeats: int = 5, extra: bool = True) -> dict:
+    import math
+
+    import cases
+
+    g = cases.gen(2)
+    lens = torch.randint(128, 4097, (N_REQ,), generator=g).tolist()
+    main = time_attention(device, lens, 4096 // BLOCK_SIZE, n_pools, iters, repeats)
     peak, which = hbm_peak()
-    achieved = alg / (us * 1e-6) / 1e9
-    return {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-            "frac": round(achieved / peak, 4), "peak_source": f"of {which}",
-            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this case under ncu
-            # (profiles/attn_decode_config2.md)
-            "traffic": 18.08e6,
-            "kernel": "attn_decode_kernel<W=2,VEC,NW=8> (fp16 m16n8k16 MMAs; one key range per row, no combine launch)",
+    roof = {"bound": "hbm", "achieved": main["achieved_GBs"], "peak": peak, "unit": "GB/s", "frac": main["frac"],
+            "peak_source": f"of {which}",
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this workload (ncu)
+            "traffic": measured_traffic(ATTN_KERNEL + "@64x[128,4096]"),
+            "kernel": ATTN_KERNEL + " (mma.sync m16n8k16 over V bits in place; equal step ranges per warp) + combine pass",
             "workload": "64 seqs ragged [128,4096] (sum %d keys), 14/2 heads, D64, T4, p=0.2, page 16, bf16 out, "
-                        "%d distinct pools back to back" % (sum_len, n_pools),
-            "us_per_launch": round(us, 2), "algorithmic_bytes": alg}
+                        "%d distinct pools back to back" % (main["sum_keys"], n_pools),
+            "us_per_launch": main["us_per_call"]["median"], "us_per_launch_spread": main["us_per_call"],
+            "algorithmic_bytes": main["algorithmic_bytes"]}
+    if extra:
+        g5 = cases.gen(5)
+        lo, hi = math.log(1024.0), math.log(32768.0)
+        ctx = torch.exp(torch.rand(64, generator=g5) * (hi - lo) + lo).long().clamp(1024, 32768).tolist()
+        roof["other_shapes"] = {
+            "256x4096_d64_14/2": time_attention(device, [4096] * 256, 256, 6, 5, repeats),
+            "64x[1k,32k]loguniform_d128_7/1 (one tensor-parallel shard of the 7B shape)":
+                time_attention(device, ctx, 2048, 4, 5, repeats, hd=128, hq=7, hkv=1),
+        }
+    return roof
 
 
-def lif_roofline(device, n_tok: int = 8192, iters: int = 10) -> dict:
+def lif_roofline(device, n_tok: int = 8192, iters: int = 10, repeats: int = 5) -> dict:
     """Fused LIF + bit-pack (+ K/V scatter) at the kernel-level configuration: gate currents bf16
     [T=4, n_tok, 4864] -> packed bits + fp32 membrane, and k/v currents [4, n_tok, 2x64x2] scattered through
-    a random slot permutation of a 16-token-page pool."""
-    from spikeinfer_b200 import kernels
+    a random slot permutation of a 16-token-page pool; both reset rules."""
+    from spikeinfer_b200 import _lib, kernels
 
     T, N, Hkv, D = 4, 4864, 2, 64
     g = torch.Generator(device=device).manual_seed(3)
@@ -268,32 +454,41 @@ def lif_roofline(device, n_tok: int = 8192, iters: int = 10) -> dict:
     def timed(fn):
         for _ in range(3):
             fn()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize(device)
-        start.record()
-        for _ in range(iters):
-            fn()
-        stop.record()
-        torch.cuda.synchronize(device)
-        return start.elapsed_time(stop) * 1e3 / iters
+        us = []
+        for _ in range(repeats):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(device)
+            start.record()
+            for _ in range(iters):
+                fn()
+            stop.record()
+            torch.cuda.synchronize(device)
+            us.append(start.elapsed_time(stop) * 1e3 / iters)
+        return us
 
     peak, which = hbm_peak()
+
+    def entry(us, alg):
+        med = statistics.median(us)
+        return {"us": stats(us, 1), "algorithmic_bytes": alg, "achieved_GBs": round(alg / med / 1e3, 1),
+                "frac": round(alg / med / 1e3 / peak, 4)}
+
     out = {}
-    us = timed(lambda: kernels.lif_pack(gate, beta, th, return_membrane=True))
-    alg = gate.numel() * 2 + gate.numel() // 8 + n_tok * N * 4
-    out["gate_pack_membrane"] = {"us": round(us, 1), "algorithmic_bytes": alg, "achieved_GBs": round(alg / us / 1e3, 1),
-                                 "frac": round(alg / us / 1e3 / peak, 4)}
-    us = timed(lambda: kernels.lif_pack(gate, beta, th))
-    alg = gate.numel() * 2 + gate.numel() // 8
-    out["gate_pack"] = {"us": round(us, 1), "algorithmic_bytes": alg, "achieved_GBs": round(alg / us / 1e3, 1),
-                        "frac": round(alg / us / 1e3 / peak, 4)}
-    us = timed(lambda: kernels.lif_pack_scatter(kv_sites))
-    alg = kv.numel() * 2 + kv.numel() // 8 + n_tok * 8
-    out["kv_pack_scatter"] = {"us": round(us, 1), "algorithmic_bytes": alg, "achieved_GBs": round(alg / us / 1e3, 1),
-                              "frac": round(alg / us / 1e3 / peak, 4)}
+    for mode, tag in ((_lib.RESET_SUBTRACT_DELAYED, "subtract_delayed"), (_lib.RESET_HARD_ZERO, "hard_zero")):
+        res = {}
+        us = timed(lambda: kernels.lif_pack(gate, beta, th, return_membrane=True, reset_mode=mode))
+        res["gate_pack_membrane"] = entry(us, gate.numel() * 2 + gate.numel() // 8 + n_tok * N * 4)
+        us = timed(lambda: kernels.lif_pack(gate, beta, th, reset_mode=mode))
+        res["gate_pack"] = entry(us, gate.numel() * 2 + gate.numel() // 8)
+        us = timed(lambda: kernels.lif_pack_scatter(kv_sites, reset_mode=mode))
+        res["kv_pack_scatter"] = entry(us, kv.numel() * 2 + kv.numel() // 8 + n_tok * 8)
+        out[tag] = res
+    out["bound"] = "hbm"
     out["peak"] = peak
     out["peak_source"] = f"of {which}"
-    out["workload"] = f"T=4, {n_tok} tokens, gate 4864 channels bf16, k/v 2 heads x 64, page 16, L2 exceeded by the gate tensor"
+    out["traffic_gate_pack_membrane"] = measured_traffic("lif_pack_scatter_vec_kernel@gate4x8192x4864+membrane")
+    out["workload"] = (f"T=4, {n_tok} tokens, gate 4864 channels bf16, k/v 2 heads x 64, page 16; the gate tensor alone "
+                       "exceeds L2; subtract_delayed is the reference's reset rule, hard_zero this library's own (parity unpinned)")
     return out
 
 
@@ -301,10 +496,15 @@ def run_kernel_bench(args) -> None:
     """Kernel-level configurations only (also the small cases the ncu captures under profiles/ run)."""
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
+    if args.attn_form != "auto":
+        from spikeinfer_b200 import _lib
+
+        form = {"general": _lib.ATTN_FORM_GENERAL, "tcgen05": _lib.ATTN_FORM_TCGEN05}[args.attn_form]
+        _lib.check(_lib.load().spk_attn_select_form(form), "spk_attn_select_form")
     if args.kernel_bench == "attn":
-        res = attention_roofline(device, n_pools=args.pools, iters=args.steps)
+        res = attention_roofline(device, n_pools=args.pools, iters=args.steps, repeats=args.repeats, extra=False)
     else:
-        res = lif_roofline(device, n_tok=args.tokens, iters=args.steps)
+        res = lif_roofline(device, n_tok=args.tokens, iters=args.steps, repeats=args.repeats)
     print(json.dumps({"kernel_bench": args.kernel_bench, **res}), flush=True)
 
 
@@ -384,58 +584,114 @@ def run_own(args) -> None:
         torch.cuda.synchronize(device)
 
     K, W = args.steps, max(args.warmup, 3)
-    engine, rates, launches_per_step, max_len = build_engine(device, seed=1234, total_steps=total_decode_steps(K, W),
-                                                             rank=rank, world=world)
+    R = max(args.repeats, 1)
+    from spikeinfer_b200.engine.replicas import max_over_ranks, shard_requests
 
-    # ---- value: tokens stay on the device --------------------------------
+    cfg, model, rates = build_model(device, seed=1234)
+    all_prompts = job_prompts(cfg, 1234, N_REQ * world)
+    mine = shard_requests(N_REQ * world, world, rank)  # this replica's share of the job's requests
+    max_len = model_len(total_decode_steps(K, W))
+    engine, launches_per_step = build_engine(model, all_prompts[mine.start:mine.stop], max_len, device)
+
+    def timed_steps(eng) -> float:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record()
+        for _ in range(K):
+            eng.decode_step()
+        stop.record()
+        barrier()
+        return start.elapsed_time(stop)
+
+    # ---- value: tokens stay on the device; the first region is the headline, the others its spread -------
     for _ in range(W):
         engine.decode_step()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+    torch.cuda.synchronize(device)
+    snap = engine.snapshot()
     with ClockSampler(local) as clocks:
         if args.profiler_range:
             torch.cuda.profiler.start()
-        start.record()
-        for _ in range(K):
-            engine.decode_step()
-        stop.record()
-        barrier()
+        ms = timed_steps(engine)
         if args.profiler_range:
             torch.cuda.profiler.stop()
-    ms = start.elapsed_time(stop)
+    regions = [ms]
+    for _ in range(R - 1):
+        engine.restore(snap)
+        regions.append(timed_steps(engine))
     # ---- e2e: host-in-the-loop steps ---------------------------------------
+    def timed_host_steps() -> float:
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(K):
+            host.copy_(engine.step_host(host))
+        torch.cuda.synchronize(device)
+        return (time.perf_counter() - t0) * 1e3
+
     host = engine.host_in
+    engine.restore(snap)
     host.copy_(engine.state.next_tokens.cpu())
     for _ in range(W):
         host.copy_(engine.step_host(host))
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(K):
-        host.copy_(engine.step_host(host))
-    torch.cuda.synchronize(device)
-    e2e_s = time.perf_counter() - t0
+    snap_host = engine.snapshot()
+    e2e_regions = []
+    for _ in range(R):
+        engine.restore(snap_host)
+        host.copy_(engine.state.next_tokens.cpu())
+        e2e_regions.append(timed_host_steps())
     engine.state.check_status()
+    # ---- strong scaling: 64 requests in the whole job ----------------------------------------------------
+    strong_ms = None
+    if world > 1 and N_REQ % world == 0:
+        share = N_REQ // world
+        small, _ = build_engine(model, all_prompts[rank * share:(rank + 1) * share], max_len, device)
+        for _ in range(W):
+            small.decode_step()
+        strong_ms = timed_steps(small)
+        del small
 
-    from spikeinfer_b200.engine.replicas import max_over_ranks
-
-    ms, e2e_ms = max_over_ranks([ms, e2e_s * 1e3], device)
+    reduced = max_over_ranks(regions + e2e_regions + ([strong_ms] if strong_ms is not None else []), device)
+    regions, e2e_regions = reduced[:R], reduced[R:2 * R]
+    ms, e2e_ms = regions[0], e2e_regions[0]
 
     if rank == 0:
-        roof = attention_roofline(device)
+        tok = N_REQ * K * world
         line = {
-            "metric": METRIC, "value": round(N_REQ * K * world / (ms * 1e-3), 1), "unit": UNIT, "n_gpus": world,
+            "metric": METRIC, "value": round(tok / (ms * 1e-3), 1), "unit": UNIT, "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": config_dict(world, max_len),
-            "e2e": {"value": round(N_REQ * K * world / (e2e_ms * 1e-3), 1), "unit": UNIT,
+            "e2e": {"value": round(tok / (e2e_ms * 1e-3), 1), "unit": UNIT,
                     "h2d_bytes_per_step": N_REQ * 8, "d2h_bytes_per_step": N_REQ * 8,
                     "ms_per_step": round(e2e_ms / K, 4)},
+            "spread": {"note": f"the same {K} steps repeated from the same batch state; value and e2e are the first region",
+                       "ms_per_step": stats([r / K for r in regions]),
+                       "tok_per_s": stats([tok / (r * 1e-3) for r in regions], 1),
+                       "e2e_ms_per_step": stats([r / K for r in e2e_regions]),
+                       "e2e_tok_per_s": stats([tok / (r * 1e-3) for r in e2e_regions], 1)},
             "gpu_launches": launches_per_step * K,
             "gpu_launches_per_step": launches_per_step,
             "clocks": clocks.summary(),
-            "roofline": roof,
             "firing_rates": {k: round(v, 3) for k, v in rates.items()},
         }
+        if strong_ms is not None:
+            strong_ms = reduced[2 * R]
+            line["strong_scaling"] = {"requests_total": N_REQ, "requests_per_gpu": N_REQ // world,
+                                      "tok_per_s": round(N_REQ * K / (strong_ms * 1e-3), 1),
+                                      "ms_per_step": round(strong_ms / K, 4)}
+        else:
+            line["strong_scaling"] = {"requests_total": N_REQ, "requests_per_gpu": N_REQ,
+                                      "tok_per_s": round(N_REQ * K / (ms * 1e-3), 1), "ms_per_step": round(ms / K, 4),
+                                      "note": "one GPU: the headline itself"}
+        del engine
+        line["roofline"] = attention_roofline(device, repeats=R)
+        line["roofline_lif"] = lif_roofline(device, repeats=R)
+        if world == 1 and not args.no_serving:
+            line["closed_loop"] = {
+                "protocol": "N requests, C in flight, 128 prompt tokens, 64 greedy output tokens, ignore_eos; prefill, "
+                            "admission, host visits and release inside the clock",
+                "runs": [closed_loop(model, cfg, device, c, n) for c, n in ((64, 128), (32, 64), (8, 32), (1, 8))],
+                "packed_prefill": closed_loop(model, cfg, device, 64, 128, packed_prefill=True)}
+            line["open_loop"] = open_loop(model, cfg, device)
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line), flush=True)
@@ -475,7 +731,7 @@ def run_reference(args) -> None:
 
 
 def run_tp7b(args) -> None:
-    """Secondary workload (BASELINE config 5): spiking Qwen2.5-7B shape (28 layers, hidden 3584, 28/4 heads,
+    """Secondary workload (the long-context tensor-parallel configuration): spiking Qwen2.5-7B shape (28 layers, hidden 3584, 28/4 heads,
     head_dim 128, MLP 18944, vocab 152064, T=4, bf16), 256 concurrent decode sequences per replica with ragged
     contexts log-uniform in [1k, 32k], head-sharded tensor parallel over min(N, 4) GPUs (NCCL all-reduce after
     o_proj and down_proj), N/4 replicas beyond that.  The pools are filled with random bits and the batch state
@@ -609,7 +865,11 @@ def main() -> None:
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--kernel-bench", choices=["attn", "lif"], default=None,
                     help="time only the kernel-level configuration of the attention or the LIF kernel")
+    ap.add_argument("--attn-form", choices=["auto", "general", "tcgen05"], default="auto",
+                    help="form of the attention kernel for --kernel-bench attn (auto: what the library picks)")
     ap.add_argument("--pools", type=int, default=24, help="distinct K/V pools of --kernel-bench attn")
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions per quantity (median, min and max are reported)")
+    ap.add_argument("--no-serving", action="store_true", help="skip the closed-loop / open-loop serving measurements")
     ap.add_argument("--tokens", type=int, default=8192, help="tokens of --kernel-bench lif")
     ap.add_argument("--workload", choices=["decode_0p5b", "tp7b"], default="decode_0p5b",
                     help="tp7b: the 7B-shape long-context tensor-parallel decode step (secondary line)")

@@ -101,6 +101,25 @@ class SpikeDecodeEngine:
         self.ledger.release(row)
         self.free_rows.append(row)
 
+    # -- snapshots (benchmarks and tests: repeat the same steps from the same state) ---------------------
+    def _state_tensors(self):
+        st = self.state
+        return (st.free_list, st._free_count, st.active, st.seq_lens, st.positions, st.slot_mapping, st.block_tables,
+                st.input_ids, st.next_tokens)
+
+    def snapshot(self) -> dict:
+        """Batch state, block ledger and free rows as they are now (the pools are not copied: steps replayed
+        from a snapshot rewrite the same slots with the same bits)."""
+        return dict(tensors=[t.clone() for t in self._state_tensors()], free=self.ledger.free,
+                    seq_lens=dict(self.ledger.seq_lens), free_rows=list(self.free_rows))
+
+    def restore(self, snap: dict) -> None:
+        for t, s in zip(self._state_tensors(), snap["tensors"]):
+            t.copy_(s)
+        self.ledger.free = snap["free"]
+        self.ledger.seq_lens = dict(snap["seq_lens"])
+        self.free_rows = list(snap["free_rows"])
+
     # -- decode -----------------------------------------------------------
     def _body(self) -> None:
         st = self.state
@@ -114,8 +133,7 @@ class SpikeDecodeEngine:
         """Capture one decode step.  Warm-up runs would advance real rows, so capture happens on a
         snapshot of the batch state and pools' pad block only: the state is saved and restored."""
         st = self.state
-        saved = [t.clone() for t in (st.free_list, st._free_count, st.active, st.seq_lens, st.positions,
-                                     st.slot_mapping, st.block_tables, st.input_ids, st.next_tokens)]
+        saved = [t.clone() for t in self._state_tensors()]
         active = st.active.clone()
         st.active.zero_()  # every row is a pad row during warm-up and capture: only the pad block is written
         side = torch.cuda.Stream(device=self.device)
@@ -128,8 +146,7 @@ class SpikeDecodeEngine:
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self._body()
-        for t, s in zip((st.free_list, st._free_count, st.active, st.seq_lens, st.positions, st.slot_mapping,
-                         st.block_tables, st.input_ids, st.next_tokens), saved):
+        for t, s in zip(self._state_tensors(), saved):
             t.copy_(s)
         st.active.copy_(active)
 

@@ -184,7 +184,7 @@ def config2_case(seed=2, n=64, lo=128, hi=4096):
 
 
 def test_config2_full_size(dev):
-    """BASELINE config 2: 64 ragged sequences in [128, 4096], 14/2 heads, D 64, T 4, Bernoulli(0.2) bits,
+    """The kernel-level attention configuration: 64 ragged sequences in [128, 4096], 14/2 heads, D 64, T 4, Bernoulli(0.2) bits,
     16-token pages in a shuffled pool.  fp32 vs the oracle at 1e-5; bf16 within 1e-3; scores exact on a sample;
     and linearity in V as a size-independent property (out(V1 | V2) = out(V1) + out(V2) for disjoint V bits)."""
     case = config2_case()

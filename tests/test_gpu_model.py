@@ -1,4 +1,4 @@
-"""GPU parity at model level (BASELINE config 1: the tiny spiking Qwen2-style decoder, fp32, page 16).
+"""GPU parity at model level (the tiny spiking Qwen2-style decoder, fp32, page 16).
 
 Layer by layer the CUDA operators are fed the oracle's own tensors, so packed K/V and LIF spikes are
 compared bit-exactly; end to end (GEMMs on cuBLAS instead of the CPU) greedy tokens must match the

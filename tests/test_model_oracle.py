@@ -1,6 +1,6 @@
 """The CPU model oracle against what the reference's own paged model path produced (engine_tiny.pt):
-greedy tokens, logits and the bit-packed K/V pools of every layer for the tiny configuration
-(BASELINE config 1), with constant and with randomised LIF parameters."""
+greedy tokens, logits and the bit-packed K/V pools of every layer for the tiny configuration,
+with constant and with randomised LIF parameters."""
 from __future__ import annotations
 
 import pytest
