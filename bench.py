@@ -400,11 +400,17 @@ def time_attention(device, lens, max_blocks, n_pools, iters, repeats, hd=64, hq=
             "frac": round(alg / med / 1e3 / peak, 4), "pools": n_pools, "sum_keys": sum(lens)}
 
 
-def attention_roofline(device, n_pools: int = 24, iters: int = 10, repeats: int = 5, extra: bool = True) -> dict:
+def attention_roofline(device, n_pools: int = 24, iters: int = 10, repeats: int = 5, extra: bool = True,
+                       uniform: tuple[int, int] | None = None) -> dict:
+    """`uniform` = (rows, keys): that many rows of equal length instead of the ragged configuration."""
     import math
 
     import cases
 
+    if uniform is not None:
+        rows, keys = uniform
+        res = time_attention(device, [keys] * rows, -(-keys // BLOCK_SIZE), n_pools, iters, repeats)
+        return {"kernel": ATTN_KERNEL, "workload": f"{rows} rows x {keys} keys, 14/2 heads, D64, T4, bf16 out, {n_pools} pools", **res}
     g = cases.gen(2)
     lens = torch.randint(128, 4097, (N_REQ,), generator=g).tolist()
     main = time_attention(device, lens, 4096 // BLOCK_SIZE, n_pools, iters, repeats)
@@ -502,7 +508,8 @@ def run_kernel_bench(args) -> None:
         form = {"general": _lib.ATTN_FORM_GENERAL, "tcgen05": _lib.ATTN_FORM_TCGEN05}[args.attn_form]
         _lib.check(_lib.load().spk_attn_select_form(form), "spk_attn_select_form")
     if args.kernel_bench == "attn":
-        res = attention_roofline(device, n_pools=args.pools, iters=args.steps, repeats=args.repeats, extra=False)
+        res = attention_roofline(device, n_pools=args.pools, iters=args.steps, repeats=args.repeats, extra=False,
+                                 uniform=(args.rows, args.keys) if args.rows and args.keys else None)
     else:
         res = lif_roofline(device, n_tok=args.tokens, iters=args.steps, repeats=args.repeats)
     print(json.dumps({"kernel_bench": args.kernel_bench, **res}), flush=True)
@@ -730,6 +737,17 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def make_tp_group(dist, rank: int, world: int, tp: int):
+    """The NCCL group of `rank`'s tensor-parallel peers: ranks [g*tp, (g+1)*tp).  Every rank creates every group, in
+    the same order, as torch.distributed requires; only its own is returned."""
+    mine = None
+    for g in range(world // tp):
+        pg = dist.new_group(list(range(g * tp, (g + 1) * tp)), backend="nccl")
+        if rank // tp == g:
+            mine = pg
+    return mine
+
+
 def run_tp7b(args) -> None:
     """Secondary workload (the long-context tensor-parallel configuration): spiking Qwen2.5-7B shape (28 layers, hidden 3584, 28/4 heads,
     head_dim 128, MLP 18944, vocab 152064, T=4, bf16), 256 concurrent decode sequences per replica with ragged
@@ -757,21 +775,21 @@ def run_tp7b(args) -> None:
         if args.verbose:
             print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
 
-    tp = min(world, 4)
+    tp = args.tp_size or min(world, 4)
     if world % tp:
-        raise SystemExit("world size must be 1, 2, 4 or a multiple of 4")
+        raise SystemExit(f"world size {world} is not a multiple of the tensor-parallel size {tp}")
     group = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-        if world == tp:
-            group = dist.group.WORLD
-        else:
-            for g in range(world // tp):  # every rank creates every group, in the same order
-                pg = dist.new_group(list(range(g * tp, (g + 1) * tp)))
-                if rank // tp == g:
-                    group = pg
-    cfg = SpikingQwenConfig(vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
-                            num_attention_heads=28, num_key_value_heads=4, head_dim=128)
+        # Exactly ONE NCCL communicator per process: the tensor-parallel group's.  The job-wide group is gloo and
+        # carries only host-side barriers and the max-reduce of the timings, after a device synchronise.  (With an
+        # NCCL job-wide group next to NCCL sub-groups, the timing loop had collectives of two communicators in
+        # flight on the same GPUs -- the job-wide barrier on its own internal stream, the sub-group's all-reduces
+        # inside the replayed graph -- with no common order across ranks, which NCCL documents as deadlock-prone.)
+        dist.init_process_group("gloo")
+        group = make_tp_group(dist, rank, world, tp) if tp > 1 else None
+    cfg = SpikingQwenConfig(vocab_size=152064, hidden_size=3584, intermediate_size=18944,
+                            num_hidden_layers=args.tp_layers or 28, num_attention_heads=28, num_key_value_heads=4,
+                            head_dim=128)
     lcfg = shard_config(cfg, tp)
     weights = random_weights_device(lcfg, device, torch.bfloat16, seed=100 + rank // tp)  # replicated parts differ per
     model = SpikingQwenModel(lcfg, weights, device=device, tp_group=group if tp > 1 else None)  # rank: irrelevant for timing
@@ -810,9 +828,10 @@ def run_tp7b(args) -> None:
     stage("decode graph captured")
 
     def barrier():
+        # device first, then the host-side (gloo) barrier: no NCCL collective besides the group's own is ever issued
+        torch.cuda.synchronize(device)
         if world > 1:
             dist.barrier()
-        torch.cuda.synchronize(device)
 
     for _ in range(W):
         engine.decode_step()
@@ -829,7 +848,22 @@ def run_tp7b(args) -> None:
         barrier()
     stage("timed steps done")
     engine.state.check_status()
-    (ms,) = max_over_ranks([start.elapsed_time(stop)], device)
+    (ms,) = max_over_ranks([start.elapsed_time(stop)], "cpu")  # host tensors: the job-wide group is gloo
+    # share of the step spent in the all-reduces: the same replays with the reduction switched off cannot be
+    # captured here (the graph holds them), so a separate loop times the bare collective on the step's tensor
+    ar_us = None
+    if tp > 1:
+        buf = torch.zeros(lcfg.T * n_seq, cfg.hidden_size, dtype=torch.bfloat16, device=device)
+        for _ in range(5):
+            dist.all_reduce(buf, group=group)
+        torch.cuda.synchronize(device)
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(20):
+            dist.all_reduce(buf, group=group)
+        a1.record()
+        torch.cuda.synchronize(device)
+        (ar_us,) = max_over_ranks([a0.elapsed_time(a1) * 1e3 / 20], "cpu")
     sum_ctx = sum(ctx)
     if rank == 0:
         kv_bytes = sum_ctx * lcfg.T * lcfg.num_key_value_heads * 2 * 4 * 4  # K+V words of one layer on one GPU
@@ -840,6 +874,9 @@ def run_tp7b(args) -> None:
             "data": "synthetic (pools pre-filled with random bits, no prefill)", "sequences_per_replica": n_seq,
             "sum_context_tokens": sum_ctx, "attention_kv_bytes_per_layer_per_gpu": kv_bytes,
             "all_reduce_bytes_per_call": lcfg.T * n_seq * cfg.hidden_size * 2, "all_reduces_per_step": 2 * cfg.num_hidden_layers if tp > 1 else 0,
+            "all_reduce_us_per_call_back_to_back": None if ar_us is None else round(ar_us, 1),
+            "all_reduce_share_of_step": None if ar_us is None else round(ar_us * 2 * cfg.num_hidden_layers / (ms / K * 1e3), 3),
+            "layers": cfg.num_hidden_layers,
             "gpu_launches_per_step": launches_per_step, "clocks": clocks.summary()}), flush=True)
     if world > 1:
         # the captured graph holds the communicator's kernels: release it before the group is torn down
@@ -868,12 +905,16 @@ def main() -> None:
     ap.add_argument("--attn-form", choices=["auto", "general", "tcgen05"], default="auto",
                     help="form of the attention kernel for --kernel-bench attn (auto: what the library picks)")
     ap.add_argument("--pools", type=int, default=24, help="distinct K/V pools of --kernel-bench attn")
+    ap.add_argument("--rows", type=int, default=0, help="--kernel-bench attn: this many rows of --keys keys each")
+    ap.add_argument("--keys", type=int, default=0)
     ap.add_argument("--repeats", type=int, default=5, help="timed regions per quantity (median, min and max are reported)")
     ap.add_argument("--no-serving", action="store_true", help="skip the closed-loop / open-loop serving measurements")
     ap.add_argument("--tokens", type=int, default=8192, help="tokens of --kernel-bench lif")
     ap.add_argument("--workload", choices=["decode_0p5b", "tp7b"], default="decode_0p5b",
                     help="tp7b: the 7B-shape long-context tensor-parallel decode step (secondary line)")
     ap.add_argument("--tp-seqs", type=int, default=256, help="sequences per replica of --workload tp7b")
+    ap.add_argument("--tp-size", type=int, default=0, help="tensor-parallel group size of --workload tp7b (default min(N, 4))")
+    ap.add_argument("--tp-layers", type=int, default=0, help="layers of --workload tp7b (default 28)")
     ap.add_argument("--verbose", action="store_true", help="print progress of the set-up stages to stderr")
     args = ap.parse_args()
     if args.workload == "tp7b" and args.impl == "own" and not args.kernel_bench:
