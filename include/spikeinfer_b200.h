@@ -85,6 +85,10 @@ const char* spk_error_string(int code);
 /* Kernels this library has launched (or recorded into a CUDA graph being captured) in this process.
  * No counterpart in the reference; used to report launch counts honestly. */
 int64_t spk_launch_count(void);
+/* 1 when the entry points that launch the decode path's kernels (attention, LIF, metadata advance, norm,
+ * argmax) wrap their launches in NVTX ranges named after themselves, else 0.  Decided once per process from
+ * the environment: SPK_NVTX set to anything but "" or "0".  No counterpart in the reference. */
+int spk_nvtx_enabled(void);
 
 /* ---------------------------------------------------------------------------
  * Bit packing.  Replaces pack_spikes / _pack_kernel and unpack_spikes

@@ -73,7 +73,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
         raise RuntimeError("nvcc failed:\n" + "\n".join(failed))
     tmp = LIB_PATH.with_suffix(".so.tmp")
     link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(tmp),
-            *map(str, objs), "-lcudart"]
+            *map(str, objs), "-lcudart", "-ldl"]
     if verbose:
         print(" ".join(link), flush=True)
     subprocess.run(link, check=True)

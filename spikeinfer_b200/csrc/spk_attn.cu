@@ -630,6 +630,7 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
                                int T, int64_t n_seqs, int num_q_heads, int num_kv_heads, int head_dim,
                                int block_size, int64_t max_blocks, int64_t num_blocks, float scale,
                                void* workspace, int64_t workspace_bytes, uint32_t* status, void* stream) {
+    SpkRange nvtx_range("spk_attn_decode");
     if (T < 0 || n_seqs < 0 || num_q_heads < 1 || num_kv_heads < 1 || max_blocks < 1 || num_blocks < 1)
         return SPK_ERR_BAD_SHAPE;
     if (num_q_heads % num_kv_heads != 0) return SPK_ERR_BAD_SHAPE;
@@ -797,6 +798,7 @@ extern "C" int spk_attn_decode_static(const int32_t* q, int64_t sq_t, int64_t sq
                                       int T, int64_t n_seqs, int num_q_heads, int num_kv_heads, int head_dim,
                                       int block_size, int64_t max_blocks, int64_t num_blocks, float scale,
                                       uint32_t* status, void* stream) {
+    SpkRange nvtx_range("spk_attn_decode_static");
     const int64_t need = spk_attn_decode_workspace_bytes(T, n_seqs, num_q_heads, num_kv_heads, head_dim,
                                                          block_size, max_blocks);
     if (need > kStaticScratchBytes) return SPK_ERR_STATIC_SCRATCH_TOO_SMALL;

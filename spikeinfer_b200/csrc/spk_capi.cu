@@ -2,11 +2,35 @@
 #include "spk_common.cuh"
 
 #include <atomic>
+#include <cstdlib>
+#include <cstring>
+
+#include <nvtx3/nvToolsExt.h>
 
 namespace {
 thread_local int g_last_cuda_error = 0;
 std::atomic<long long> g_launches{0};
 }
+
+namespace {
+bool nvtx_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("SPK_NVTX");
+        return v != nullptr && std::strcmp(v, "0") != 0 && v[0] != '\0';
+    }();
+    return on;
+}
+}  // namespace
+
+SpkRange::SpkRange(const char* name) : on(nvtx_enabled()) {
+    if (on) nvtxRangePushA(name);
+}
+
+SpkRange::~SpkRange() {
+    if (on) nvtxRangePop();
+}
+
+extern "C" int spk_nvtx_enabled(void) { return nvtx_enabled() ? 1 : 0; }
 
 void spk_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 

@@ -22,6 +22,16 @@ void spk_count_launch();
         spk_count_launch();                              \
     } while (0)
 
+// NVTX range around an entry point's launches, for timelines taken with a profiler.  Off unless the
+// environment holds SPK_NVTX=1 when the library makes its first call (defined in spk_capi.cu).
+struct SpkRange {
+    explicit SpkRange(const char* name);
+    ~SpkRange();
+    SpkRange(const SpkRange&) = delete;
+    SpkRange& operator=(const SpkRange&) = delete;
+    bool on;
+};
+
 static inline cudaStream_t spk_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
 // Up to SPK_MAX_DIMS leading dimensions of a strided array, innermost last.

@@ -710,6 +710,7 @@ extern "C" int spk_lif(const void* x, int x_dtype, int T, int64_t stride_t, int 
                        const int64_t* mid_sizes, const int64_t* mid_strides, int64_t N,
                        const float* beta, const float* threshold, const float* mem0, void* spikes,
                        int spike_dtype, float* mem_out, int reset_mode, void* stream) {
+    SpkRange nvtx_range("spk_lif");
     if (T < 0 || N <= 0) return SPK_ERR_BAD_SHAPE;
     if (reset_mode != SPK_RESET_SUBTRACT_DELAYED && reset_mode != SPK_RESET_HARD_ZERO)
         return SPK_ERR_UNSUPPORTED;
@@ -754,6 +755,7 @@ extern "C" int spk_lif(const void* x, int x_dtype, int T, int64_t stride_t, int 
 
 extern "C" int spk_lif_pack_scatter(const spk_lif_site* sites, int n_sites, int T, int64_t n_tok,
                                     int reset_mode, uint32_t* status, void* stream) {
+    SpkRange nvtx_range("spk_lif_pack_scatter");
     if (sites == nullptr) return SPK_ERR_NULL_POINTER;
     if (n_sites < 1 || n_sites > SPK_MAX_LIF_SITES || T < 1 || n_tok < 0) return SPK_ERR_BAD_SHAPE;
     if (reset_mode != SPK_RESET_SUBTRACT_DELAYED && reset_mode != SPK_RESET_HARD_ZERO)

@@ -196,6 +196,7 @@ extern "C" int spk_meta_advance(int32_t* free_list, int32_t* free_count, const i
                                 int32_t* block_tables, int64_t* input_ids, const int64_t* next_tokens,
                                 int32_t max_rows, int32_t max_blocks, int32_t pad_block,
                                 int32_t block_size, uint32_t* status, void* stream) {
+    SpkRange nvtx_range("spk_meta_advance");
     if (max_rows < 1 || max_rows > kMaxRows || max_blocks < 1 || block_size < 1) return SPK_ERR_BAD_SHAPE;
     if (free_list == nullptr || free_count == nullptr || active == nullptr || seq_lens == nullptr ||
         positions == nullptr || slot_mapping == nullptr || block_tables == nullptr || input_ids == nullptr)

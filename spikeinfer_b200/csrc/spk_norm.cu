@@ -154,6 +154,7 @@ int launch_norm(void* h, const void* delta, const void* weight, float eps, void*
 
 extern "C" int spk_add_rmsnorm(void* h, const void* delta, const void* weight, float eps, void* out, int64_t rows,
                                int64_t hidden, int dtype, void* stream) {
+    SpkRange nvtx_range("spk_add_rmsnorm");
     if (rows < 0 || hidden < 1 || hidden > 0x7fffffffLL) return SPK_ERR_BAD_SHAPE;
     if (rows == 0) return SPK_OK;
     if (h == nullptr || weight == nullptr || out == nullptr) return SPK_ERR_NULL_POINTER;

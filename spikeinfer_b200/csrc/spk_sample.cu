@@ -147,6 +147,7 @@ extern "C" int64_t spk_argmax_workspace_bytes(int64_t rows) {
 
 extern "C" int spk_argmax(const void* x, int dtype, int64_t rows, int64_t cols, int64_t row_stride, int64_t* out,
                           void* workspace, int64_t workspace_bytes, void* stream) {
+    SpkRange nvtx_range("spk_argmax");
     if (rows < 0 || cols < 1 || row_stride < cols) return SPK_ERR_BAD_SHAPE;
     if (dtype != SPK_F32 && dtype != SPK_BF16 && dtype != SPK_F16) return SPK_ERR_BAD_DTYPE;
     if (rows == 0) return SPK_OK;

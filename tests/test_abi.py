@@ -133,3 +133,18 @@ def test_operator_surface_matches_the_reference():
             assert defaults[f["name"]] == f["has_default"], f["name"]
     for extra in mine[len(theirs):]:
         assert defaults[extra], f"extra metadata field {extra} needs a default"
+
+
+def test_nvtx_ranges_follow_the_environment():
+    """SPK_NVTX switches the NVTX ranges of the entry points on; the default is off (one fresh process each)."""
+    import os
+    import subprocess
+    import sys
+    code = "from spikeinfer_b200 import _lib; print(_lib.load().spk_nvtx_enabled())"
+    root = str(Path(__file__).resolve().parent.parent)
+    for value, want in ((None, "0"), ("1", "1"), ("0", "0")):
+        env = {k: v for k, v in os.environ.items() if k != "SPK_NVTX"}
+        if value is not None:
+            env["SPK_NVTX"] = value
+        out = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, check=True)
+        assert out.stdout.strip().splitlines()[-1] == want
