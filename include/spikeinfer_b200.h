@@ -217,8 +217,9 @@ int spk_argmax(const void* x, int dtype, int64_t rows, int64_t cols, int64_t row
  * (22 significant bits; within 1e-6 of a float64 evaluation, relative to the largest output);
  * for BF16/F16 output one fp16 weight is used in numerator and denominator alike (within 1e-3
  * before the rounding to the output type).  K and V are read once per KV head, shared by the
- * H_q/H_kv query heads of the group.  Rows are cut into key ranges (512-key units when pages are
- * contiguous 16-byte aligned rows at head_dim 64/128) whose partial sums live in `workspace`
+ * H_q/H_kv query heads of the group.  Rows longer than 256 keys may be cut into key ranges (equal
+ * shares of the call's 32-key steps per warp when pages are contiguous 16-byte aligned rows at
+ * head_dim 64/128, else ranges per row) whose partial sums live in `workspace`
  * (size from spk_attn_decode_workspace_bytes with the same arguments; may be NULL when that
  * returns 0).  head_dim must be a multiple of 32, <= 128; block_size a power of two, >= 1;
  * 0 <= scale and scale * head_dim <= 24 (head_dim^-0.5, the reference's scale, always is), else
@@ -260,10 +261,12 @@ int spk_attn_select_form(int form);
  *
  *  - No cudaMalloc / cudaFree and no other allocating call is made, here or on first use.
  *  - A problem whose spk_attn_decode_workspace_bytes() exceeds spk_attn_decode_static_capacity()
- *    is refused with SPK_ERR_STATIC_SCRATCH_TOO_SMALL and nothing is launched.  Sequences of up to
- *    512 keys need no scratch at all; 48 sequences of up to 4096 keys at T=4, 14/2 heads,
- *    head_dim 64 need 6.4 MB (one 2080-byte record per sequence, timestep, KV head and 512-key unit)
- *    and fit, 64 such sequences (8.5 MB) do not.
+ *    is refused with SPK_ERR_STATIC_SCRATCH_TOO_SMALL and nothing is launched.  Tables of up to
+ *    256 keys per sequence (max_blocks * block_size) need no scratch at all.  Beyond that the need
+ *    grows with n_seqs * T * H_kv * max_blocks * block_size (two records of 8 * head_dim + 8 floats
+ *    per warp that shares the work, up to 2960 warps, plus the rows' step prefix): at T=4, 14/2
+ *    heads, head_dim 64, 15 sequences of up to 4096 keys need 7.99 MB and fit, 16 such sequences
+ *    (8.52 MB) do not.
  *  - The first call on each device, whatever its sizes (a problem that needs no scratch included),
  *    looks up the array's device address with that device current and remembers it; make that
  *    first call during start-up, before any stream capture begins.  Later calls only read the

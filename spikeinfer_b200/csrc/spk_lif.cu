@@ -91,6 +91,66 @@ struct Lif {
     }
 };
 
+// Four timesteps of ONE channel from a zero membrane, channel-major: the spike predicate of a step is consumed by
+// the next step's reset directly (`@p sub` / `@p mov`), so it lives for a handful of instructions and no register
+// holds a reset term.  Same values as four Lif::step calls after init(0, th): u - 0 = u exactly, and the first
+// step's beta * 0 + x is x + 0 for the finite beta >= 0 that clamp_beta guarantees.  Five instructions per
+// element-step (four in the first) against six.
+template <int MODE, uint32_t BIT>
+__device__ __forceinline__ float lif_chain4(float x0, float x1, float x2, float x3, float beta, float th,
+                                            uint32_t& b0, uint32_t& b1, uint32_t& b2, uint32_t& b3) {
+    float u;
+    if (MODE == SPK_RESET_SUBTRACT_DELAYED) {
+        asm("{\n\t.reg .pred p;\n\t"
+            "setp.gt.f32 p, 0f00000000, %6;\n\t"
+            "add.rn.f32 %0, %7, 0f00000000;\n\t"
+            "@p sub.rn.f32 %0, %0, %6;\n\t"
+            "setp.gt.f32 p, %0, %6;\n\t"
+            "@p or.b32 %1, %1, %11;\n\t"
+            "mul.rn.f32 %0, %5, %0;\n\t"
+            "add.rn.f32 %0, %0, %8;\n\t"
+            "@p sub.rn.f32 %0, %0, %6;\n\t"
+            "setp.gt.f32 p, %0, %6;\n\t"
+            "@p or.b32 %2, %2, %11;\n\t"
+            "mul.rn.f32 %0, %5, %0;\n\t"
+            "add.rn.f32 %0, %0, %9;\n\t"
+            "@p sub.rn.f32 %0, %0, %6;\n\t"
+            "setp.gt.f32 p, %0, %6;\n\t"
+            "@p or.b32 %3, %3, %11;\n\t"
+            "mul.rn.f32 %0, %5, %0;\n\t"
+            "add.rn.f32 %0, %0, %10;\n\t"
+            "@p sub.rn.f32 %0, %0, %6;\n\t"
+            "setp.gt.f32 p, %0, %6;\n\t"
+            "@p or.b32 %4, %4, %11;\n\t}"
+            : "=&f"(u), "+r"(b0), "+r"(b1), "+r"(b2), "+r"(b3)
+            : "f"(beta), "f"(th), "f"(x0), "f"(x1), "f"(x2), "f"(x3), "n"(BIT));
+    } else {
+        asm("{\n\t.reg .pred p;\n\t"
+            "add.rn.f32 %0, %7, 0f00000000;\n\t"
+            "setp.gt.f32 p, %0, %6;\n\t"
+            "@p or.b32 %1, %1, %11;\n\t"
+            "@p mov.f32 %0, 0f00000000;\n\t"
+            "mul.rn.f32 %0, %5, %0;\n\t"
+            "add.rn.f32 %0, %0, %8;\n\t"
+            "setp.gt.f32 p, %0, %6;\n\t"
+            "@p or.b32 %2, %2, %11;\n\t"
+            "@p mov.f32 %0, 0f00000000;\n\t"
+            "mul.rn.f32 %0, %5, %0;\n\t"
+            "add.rn.f32 %0, %0, %9;\n\t"
+            "setp.gt.f32 p, %0, %6;\n\t"
+            "@p or.b32 %3, %3, %11;\n\t"
+            "@p mov.f32 %0, 0f00000000;\n\t"
+            "mul.rn.f32 %0, %5, %0;\n\t"
+            "add.rn.f32 %0, %0, %10;\n\t"
+            "setp.gt.f32 p, %0, %6;\n\t"
+            "@p or.b32 %4, %4, %11;\n\t"
+            "@p mov.f32 %0, 0f00000000;\n\t}"
+            : "=&f"(u), "+r"(b0), "+r"(b1), "+r"(b2), "+r"(b3)
+            : "f"(beta), "f"(th), "f"(x0), "f"(x1), "f"(x2), "f"(x3), "n"(BIT));
+    }
+    return u;
+}
+
 // ORs the bytes of the four lanes that build one packed word (lane & 3 = byte position) into every one of
 // them.  A shuffle under a mask that differs between lanes is expanded by the compiler into a match/vote loop
 // over the distinct masks (measured: ~7 of 17.8 instructions per element of the fused kernel), so a warp whose
@@ -216,6 +276,14 @@ struct Raw8<__half> {
     }
 };
 
+
+// Four timesteps of the 8 channels of a segment, channel by channel; bit c of bits[t] = spike of channel c at t.
+template <int MODE, typename TX, int... C>
+__device__ __forceinline__ void chain8(const Raw8<TX> (&raw)[4], const float (&b)[8], const float (&th)[8],
+                                       float (&u)[8], uint32_t (&bits)[4], std::integer_sequence<int, C...>) {
+    ((u[C] = lif_chain4<MODE, (1u << C)>(raw[0].get(C), raw[1].get(C), raw[2].get(C), raw[3].get(C), b[C], th[C],
+                                          bits[0], bits[1], bits[2], bits[3])), ...);
+}
 
 // One timestep of the 8 channels of a segment; bit c of `bits` = spike of channel c.
 template <int MODE, typename TX, int... C>
@@ -348,6 +416,9 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
     const bool has_packed = s.packed != nullptr, has_dense = !PLAIN && s.dense != nullptr;
     const bool has_gated = !PLAIN && s.gated != nullptr;
     const unsigned group_mask = 0xFu << (lane & 28);  // the four lanes that build one word together
+    // byte selectors of the two exchange rounds of the 4 x 4 byte transpose (streaming plain form)
+    const uint32_t sel_a = (lane & 1) ? 0x3715u : 0x6240u;  // even lane keeps timesteps 0 and 2 of its pair, odd 1 and 3
+    const uint32_t sel_b = (lane & 2) ? 0x3276u : 0x5410u;  // then the lower pair keeps the lower timestep
 
     constexpr int VECS = sizeof(TX) * kSeg / 16;  // 16-byte pieces of one 8-channel segment
     auto issue = [&](int jj) {
@@ -429,7 +500,30 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
             for (int c = 0; c < kSeg; ++c) { rc[c] = cr.get(c); rs[c] = sr.get(c); }
         }
 
-        if (ASYNC) {
+        if (ASYNC && PLAIN && FULL) {
+            // Streaming form, nothing but bits (and the final membrane) asked for: the four timesteps of the
+            // token come out of this lane's shared-memory slots together and every channel runs its four steps
+            // in one go (lif_chain4).  The 4 x 4 bytes (lane of the word x timestep) are then transposed across
+            // the word's four lanes in two exchange rounds, so that lane `sub` ends up with timestep `sub`'s word.
+            const uint4* mine_stage = stage + (j % kStages) * slots * 32;
+            Raw8<TX> raw[kStepGroup];
+#pragma unroll
+            for (int i = 0; i < kStepGroup; ++i) raw[i].from_smem(mine_stage + i * VECS * 32);
+            float uf[kSeg];
+            uint32_t bits[kStepGroup] = {0, 0, 0, 0};
+            chain8<MODE, TX>(raw, b, th, uf, bits, std::make_integer_sequence<int, kSeg>{});
+#pragma unroll
+            for (int c = 0; c < kSeg; ++c) st[c].u = uf[c];
+            uint32_t mine = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+            if (all_live) {
+                mine = __byte_perm(mine, __shfl_xor_sync(0xffffffffu, mine, 1), sel_a);
+                mine = __byte_perm(mine, __shfl_xor_sync(0xffffffffu, mine, 2), sel_b);
+            } else {
+                mine = __byte_perm(mine, __shfl_xor_sync(group_mask, mine, 1), sel_a);
+                mine = __byte_perm(mine, __shfl_xor_sync(group_mask, mine, 2), sel_b);
+            }
+            if (wp != nullptr) *wp = mine;
+        } else if (ASYNC) {
             // Streaming form: one timestep at a time straight from this lane's shared-memory slots (T <= 4),
             // rolled loop: few live registers, small code.
             const uint4* mine_stage = stage + (j % kStages) * slots * 32;
