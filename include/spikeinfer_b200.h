@@ -238,6 +238,17 @@ int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int64_t sq_h,
                     int block_size, int64_t max_blocks, int64_t num_blocks, float scale,
                     void* workspace, int64_t workspace_bytes, uint32_t* status, void* stream);
 
+/* Lets the NEXT spk_attn_decode / spk_attn_decode_static call of this host thread overlap the launch that
+ * precedes it on its stream (programmatic dependent launch): the attention grid is placed while that launch
+ * still runs, reads seq_lens and block_tables, and waits for the launch to finish before it touches q, the
+ * pools, the workspace or `out`.  The caller vouches that seq_lens and block_tables were complete before the
+ * preceding launch BEGAN (in a decode step they are written at the head of the step, and the preceding launch is
+ * spk_lif_pack_scatter, which produces q and the newest K/V rows).  One-shot: it applies to one call and is
+ * cleared by it, also when that call returns an error.  Results are the same with and without it.  Returns
+ * SPK_OK.  No
+ * counterpart in the reference. */
+int spk_attn_overlap_next_call(void);
+
 /* Which form of the attention kernel spk_attn_decode takes (no counterpart in the reference; it lets tests and
  * benchmarks run one form against another).  AUTO: the streaming mma.sync form where the layout allows it
  * (pages of contiguous, 16-byte aligned rows, head_dim 64 or 128), else the general form.  GENERAL: always the

@@ -92,6 +92,7 @@ SIGNATURES = {
     "spk_error_string": (c_char_p, [c_int]),
     "spk_launch_count": (c_int64, []),
     "spk_nvtx_enabled": (c_int, []),
+    "spk_attn_overlap_next_call": (c_int, []),
     "spk_pack": (c_int, [c_void_p, c_int, c_int, I64P, I64P, c_int64, c_void_p, c_void_p]),
     "spk_unpack": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p]),
     "spk_lif": (c_int, [c_void_p, c_int, c_int, c_int64, c_int, I64P, I64P, c_int64, c_void_p,

@@ -41,6 +41,10 @@ class AttentionMetadata:
     chunks run through the packed popcount kernel in one batched launch instead of per-sequence SDPA."""
     prefill_row_lens: torch.Tensor | None = None
     """int32 ``[n_prefill_tok]``: keys visible to each prefill token (context + position in chunk + 1)."""
+    tables_settled: bool = False
+    """The caller vouches that ``block_tables`` and ``seq_lens`` were complete before the launch that precedes the
+    decode attention on the stream began (they are written at the head of the step).  The attention launch of
+    :func:`fused_qkv_attention` may then overlap the tail of the LIF launch before it."""
 
     @property
     def num_prefills(self) -> int:
@@ -57,7 +61,8 @@ class AttentionMetadata:
             seq_lens=mv(self.seq_lens), prefill_query_starts=self.prefill_query_starts,
             prefill_query_lens=self.prefill_query_lens, prefill_context_lens=self.prefill_context_lens,
             prefill_block_tables=[mv(t) for t in self.prefill_block_tables], status=mv(self.status),
-            prefill_row_tables=mv(self.prefill_row_tables), prefill_row_lens=mv(self.prefill_row_lens))
+            prefill_row_tables=mv(self.prefill_row_tables), prefill_row_lens=mv(self.prefill_row_lens),
+            tables_settled=self.tables_settled)
 
 
 def build_prefill_rows(meta: AttentionMetadata, pad_block: int = 0) -> AttentionMetadata:
@@ -189,9 +194,10 @@ def fused_qkv_attention(qkv: torch.Tensor, lif_q, lif_k, lif_v, k_cache, v_cache
     out = torch.empty((T, n_tok, hq, d), device=device, dtype=dtype)
     n_dec = meta.num_decode_tokens
     if n_dec:
+        # directly behind the LIF launch: nothing but allocations in between
         paged_spike_attn_decode(q_packed[:, :n_dec], k_cache, v_cache, meta.block_tables, meta.seq_lens,
                                 head_dim=d, block_size=meta.block_size, num_q_heads=hq, num_kv_heads=hkv,
-                                out=out[:, :n_dec], status=meta.status)
+                                out=out[:, :n_dec], status=meta.status, overlap_previous=meta.tables_settled)
     if packed_prefill:
         n_pre = meta.prefill_row_lens.numel()
         paged_spike_attn_decode(q_packed[:, n_dec:n_dec + n_pre], k_cache, v_cache, meta.prefill_row_tables,

@@ -605,6 +605,15 @@ gather_unpack_kernel(const uint32_t* __restrict__ cache, int64_t s_t, int64_t s_
 
 }  // namespace
 
+namespace {
+thread_local bool g_overlap_next_call = false;
+}
+
+extern "C" int spk_attn_overlap_next_call(void) {
+    g_overlap_next_call = true;
+    return SPK_OK;
+}
+
 extern "C" int64_t spk_attn_decode_workspace_bytes(int T, int64_t n_seqs, int num_q_heads,
                                                    int num_kv_heads, int head_dim, int block_size,
                                                    int64_t max_blocks) {
@@ -631,6 +640,8 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
                                int block_size, int64_t max_blocks, int64_t num_blocks, float scale,
                                void* workspace, int64_t workspace_bytes, uint32_t* status, void* stream) {
     SpkRange nvtx_range("spk_attn_decode");
+    const bool overlap = g_overlap_next_call;  // one-shot, consumed whatever happens below
+    g_overlap_next_call = false;
     if (T < 0 || n_seqs < 0 || num_q_heads < 1 || num_kv_heads < 1 || max_blocks < 1 || num_blocks < 1)
         return SPK_ERR_BAD_SHAPE;
     if (num_q_heads % num_kv_heads != 0) return SPK_ERR_BAD_SHAPE;
@@ -667,6 +678,7 @@ extern "C" int spk_attn_decode(const int32_t* q, int64_t sq_t, int64_t sq_n, int
     p.bs_log2 = bs_log2; p.max_keys = static_cast<int>(max_blocks << bs_log2); p.num_blocks = static_cast<int>(num_blocks);
     p.scale = scale; p.ws = static_cast<float*>(workspace); p.splits = pl.splits; p.granule = 32 * pl.warps;
     p.status = status;
+    p.overlap = overlap ? 1 : 0;
     p.items = n_seqs * T * num_kv_heads * pl.passes * pl.splits;
     // all CTAs resident at once: their order does not matter, and skipping the ranking takes one dependent
     // global load off the start of every CTA

@@ -18,6 +18,7 @@ struct AttnParams {
     float* ws; int splits; int granule;  // granule: keys per CTA step = 32 x warps per CTA (general form)
     int longest_first;  // rank rows by length in-kernel (only worth its dependent load when CTAs outnumber the slots)
     uint32_t* status;
+    int overlap;  // the caller allows this launch to overlap the previous one on the stream (see spk_attn_overlap_next_call)
     int64_t items;
 };
 
@@ -29,6 +30,7 @@ struct StreamPlan {
     bool ok;            // the shape is one the streaming form handles
     bool dense;         // range form: the warps of the grid share one list of 32-key steps in equal parts
     bool cut;           // range form: some item may be cut between warps (records and a combine pass exist)
+    int short_steps;    // range form: items of at most this many 32-key steps are never cut
     int64_t workers;    // range form: warps sharing the list
     int unit_keys;      // unit form: keys per unit (512, 1024 or 2048)
     int max_units;      // unit form: units of the longest possible row

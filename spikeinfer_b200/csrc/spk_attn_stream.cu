@@ -44,6 +44,7 @@ constexpr int kResidentWarpsTarget = 148 * 20;
 constexpr int kXGroup = 32 * 4 + 16;  // words between two groups of four byte-words in the regrouped V tile (padded: bank spread)
 
 struct StreamParams {
+    int short_steps;  // range form: an item of at most this many 32-key steps is never cut between warps
     int unit_log2;    // log2 of the keys per unit (unit form)
     int max_units;    // units of the longest possible row (unit form)
     int gt;           // T * Hkv * passes: items per sequence
@@ -186,6 +187,8 @@ __device__ __forceinline__ void store_channels(TO* dst, const float* src, float 
 #endif
 
 constexpr int kShortSteps = 8;   // an item of at most this many 32-key steps (256 keys) is never cut between warps
+constexpr int kUncutSteps = 24;  // tables of at most this many steps (768 keys): nothing is cut at all.  One warp walks such
+                                 // a row in under 5 us, about what the combine pass adds to a call once anything may be cut
 
 template <int W>
 struct StreamSmem {
@@ -215,14 +218,41 @@ __device__ __forceinline__ void stream_piece(const AttnParams& p, const StreamPa
     const int h0 = g * p.n_rep + pass * kAttnHeads;
     const int nh = min(kAttnHeads, p.n_rep - pass * kAttnHeads);
 
+    const int bs_mask = (1 << p.bs_log2) - 1;
+    const int span = kTblMax << p.bs_log2;  // keys whose block-table entries fit the staging
+    // block-table entries of the stretch [c0, c1) into this warp's staging
+    auto stage_tables = [&](int c0, int c1) {
+        const int page0 = c0 >> p.bs_log2;
+        const int last_page = ((c1 - 1) >> p.bs_log2) - page0;
+        const int32_t* table = p.tables + row * p.sbt_n + page0;
+        for (int i = lane; i <= last_page; i += 32) {
+            int32_t ph = __ldg(table + i);
+            if (static_cast<uint32_t>(ph) >= static_cast<uint32_t>(p.num_blocks)) {
+                spk_flag(p.status, SPK_STATUS_BAD_BLOCK);
+                ph = 0;
+            }
+            tbl[i] = ph;
+        }
+    };
     // query words of this thread's head and their popcount (the softmax bound)
     uint32_t qw[W];
+    auto load_q = [&]() {
+#pragma unroll
+        for (int w = 0; w < W; ++w)
+            qw[w] = gid < nh ? __ldg(p.q + t * p.sq_t + row * p.sq_n + (h0 + gid) * p.sq_h + w) : 0u;
+    };
+    if (!p.overlap) load_q();  // in flight together with the table entries
+    __syncwarp();  // every lane is done with the previous piece's entries
+    stage_tables(key0, min(kend, key0 + span));
+    if (p.overlap) {
+        // Everything above read lengths and block tables only.  q and the newest K/V rows come from the kernel
+        // launched just before this one, which this launch overlaps (programmatic dependent launch): wait for it.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        load_q();
+    }
     int cmax = 0;
 #pragma unroll
-    for (int w = 0; w < W; ++w) {
-        qw[w] = gid < nh ? __ldg(p.q + t * p.sq_t + row * p.sq_n + (h0 + gid) * p.sq_h + w) : 0u;
-        cmax += __popc(qw[w]);
-    }
+    for (int w = 0; w < W; ++w) cmax += __popc(qw[w]);
     const uint32_t* my_rlut = rlut + (D - cmax);
     uint32_t ones[4];  // fp16 {1, 1}: the left operand of the weight totals (kept in registers, opaque to the compiler)
 #pragma unroll
@@ -236,8 +266,6 @@ __device__ __forceinline__ void stream_piece(const AttnParams& p, const StreamPa
     const uint32_t ring_addr = static_cast<uint32_t>(__cvta_generic_to_shared(ring)) + lane * 16;
     const uint32_t* kbase = p.k + t * p.sk_t + g * p.sk_h;
     const uint32_t* vbase = p.v + t * p.sv_t + g * p.sv_h;
-    const int bs_mask = (1 << p.bs_log2) - 1;
-    const int span = kTblMax << p.bs_log2;  // keys whose block-table entries fit the staging
 
     // the piece in stretches of at most `span` keys: block-table entries staged once per stretch
     for (int c0 = key0; c0 < kend; c0 += span) {
@@ -246,17 +274,9 @@ __device__ __forceinline__ void stream_piece(const AttnParams& p, const StreamPa
         const int ntiles = (nkeys + kTileKeys - 1) / kTileKeys;
         const int page0 = c0 >> p.bs_log2;
         const int last_page = ((c1 - 1) >> p.bs_log2) - page0;
-        __syncwarp();  // every lane is done with the previous stretch's entries and ring
-        {
-            const int32_t* table = p.tables + row * p.sbt_n + page0;
-            for (int i = lane; i <= last_page; i += 32) {
-                int32_t ph = __ldg(table + i);
-                if (static_cast<uint32_t>(ph) >= static_cast<uint32_t>(p.num_blocks)) {
-                    spk_flag(p.status, SPK_STATUS_BAD_BLOCK);
-                    ph = 0;
-                }
-                tbl[i] = ph;
-            }
+        if (c0 != key0) {
+            __syncwarp();  // every lane is done with the previous stretch's entries and ring
+            stage_tables(c0, c1);
         }
         __syncwarp();
         // copies: W = 2: lane l moves keys 2l, 2l+1 of the 64-key tile (16 bytes of K, 16 of V);
@@ -413,7 +433,7 @@ __device__ __forceinline__ int64_t range_of(const RangeSplit& r, int64_t x) {
 
 // DENSE (up to kDenseRows sequences): the work of the whole call is one list of 32-key steps, ordered by item;
 // the warps of the grid cut it into equal consecutive ranges, so every warp carries the same number of steps
-// whatever the mix of row lengths.  A short item (at most kShortSteps steps) is never cut: it belongs, whole, to
+// whatever the mix of row lengths.  A short item (at most sp.short_steps steps) is never cut: it belongs, whole, to
 // the range it starts in.  A warp therefore works on a few pieces: whole items (written straight to the output)
 // and at most two cut ones, the item that began before its range (record slot 0) and the one that continues
 // after it (slot 1).
@@ -494,8 +514,11 @@ attn_stream_kernel(const AttnParams p, const StreamParams sp) {
 
     if (DENSE) {
         // the first CTA leaves the step prefix where the combine pass finds it
-        if (blockIdx.x == 0 && sp.prefix_out != nullptr)
+        if (blockIdx.x == 0 && sp.prefix_out != nullptr) {
+            // when this launch overlaps the one before it, the previous call's combine pass may still read its copy
+            if (p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int i = threadIdx.x; i <= n_seqs; i += kThreads) sp.prefix_out[i] = prefix[i];
+        }
         if (worker >= sp.workers) return;
         const int64_t total = static_cast<int64_t>(prefix[n_seqs]) * sp.gt;
         // this warp's range of the step list; a short item belongs, whole, to the range it starts in
@@ -505,7 +528,7 @@ attn_stream_kernel(const AttnParams p, const StreamParams sp) {
         bool first = true;
         while (gs < gend) {
             const StepPos at = locate_step(prefix, n_seqs, sp.gt, gs);
-            const bool is_short = at.nsteps <= kShortSteps;
+            const bool is_short = at.nsteps <= sp.short_steps;
             if (first && is_short && at.step > 0) {  // started in the previous range: not ours
                 gs += at.nsteps - at.step;
                 first = false;
@@ -930,12 +953,14 @@ attn_tc_kernel(const AttnParams p, const StreamParams sp) {
 // the records' values are fetched four records at a time (independent loads) and added in record order.
 __global__ void __launch_bounds__(128)
 attn_stream_combine_kernel(const AttnParams p, const StreamParams sp, int D) {
+    // a following launch that asked to overlap (it waits for this grid before it touches q, K/V or the records)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int64_t item = blockIdx.x;  // row * gt_count + gt
     const int gt = static_cast<int>(item % sp.gt);
     const int64_t row = item / sp.gt;
     const int len = clamp_len(__ldg(p.lens + row), p.max_keys);
     if (sp.dense) {
-        if (steps_of(len) <= kShortSteps) return;  // never cut
+        if (steps_of(len) <= sp.short_steps) return;  // never cut
     } else if (units_of(len, sp.unit_log2) <= 1) {
         return;
     }
@@ -1005,10 +1030,24 @@ static inline int log2_exact(int x) {
 }
 
 template <int W, int NB>
-int launch_stream(const AttnParams& p, const StreamParams& sp, int64_t ctas, cudaStream_t stream) {
-    if (sp.dense) attn_stream_kernel<W, NB, true><<<static_cast<unsigned>(ctas), kThreads, 0, stream>>>(p, sp);
-    else attn_stream_kernel<W, NB, false><<<static_cast<unsigned>(ctas), kThreads, 0, stream>>>(p, sp);
-    SPK_CHECK_LAUNCH();
+int launch_stream(const AttnParams& p, const StreamParams& sp, int64_t ctas, bool overlap, cudaStream_t stream) {
+    // overlap: the caller vouches that lengths and block tables were complete before the PREVIOUS launch on
+    // this stream began, so this grid may be placed while that launch still runs (programmatic stream
+    // serialisation); the kernel reads nothing else before its griddepcontrol.wait.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(ctas));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    const cudaError_t e = sp.dense ? cudaLaunchKernelEx(&cfg, attn_stream_kernel<W, NB, true>, p, sp)
+                                   : cudaLaunchKernelEx(&cfg, attn_stream_kernel<W, NB, false>, p, sp);
+    if (e != cudaSuccess) return spk_set_cuda_error(e);
+    spk_count_launch();
     return SPK_OK;
 }
 
@@ -1063,7 +1102,7 @@ StreamPlan spk_attn_stream_plan(int T, int64_t n_seqs, int Hq, int Hkv, int head
 
     // range form (up to kDenseRows sequences): the step list is shared by `workers` warps, at least eight steps
     // each if every row were full, at most what the GPU holds at once; two record slots per worker and the step
-    // prefix, needed only if some item can be longer than kShortSteps steps
+    // prefix, needed only if some item can be cut (pl.short_steps)
     pl.dense = n_seqs <= kDenseRows;
     int64_t range_bytes = 0;
     if (pl.dense) {
@@ -1073,7 +1112,8 @@ StreamPlan spk_attn_stream_plan(int T, int64_t n_seqs, int Hq, int Hkv, int head
         int64_t workers = (all_steps + 7) / 8;
         workers = workers < 1 ? 1 : (workers > cap ? cap : workers);
         pl.workers = workers;
-        pl.cut = max_steps > kShortSteps;
+        pl.short_steps = max_steps <= kUncutSteps ? static_cast<int>(max_steps) : kShortSteps;
+        pl.cut = max_steps > pl.short_steps;
         if (pl.cut) range_bytes = ((workers * 2 * rec_bytes + 15) / 16) * 16 + (n_seqs + 1) * static_cast<int64_t>(sizeof(int));
     }
     // the tcgen05 form (selectable at head_dim 64) uses the unit records
@@ -1122,6 +1162,7 @@ int spk_attn_stream_launch(const AttnParams& p, const StreamPlan& plan, int head
     sp.gt = p.T * p.Hkv * plan.passes;
     sp.dense = plan.dense;
     sp.rec = plan.rec_floats;
+    sp.short_steps = plan.short_steps;
     const int esize = p.out_dtype == SPK_F32 ? 4 : 2;
     const int per = 16 / esize;
     sp.out_vec = reinterpret_cast<uintptr_t>(p.out) % 16 == 0 && p.so_t % per == 0 && p.so_n % per == 0 && p.so_h % per == 0;
@@ -1151,6 +1192,7 @@ int spk_attn_stream_launch(const AttnParams& p, const StreamPlan& plan, int head
         return plan.max_units > 1 ? launch_combine(p, sp, head_dim, stream) : SPK_OK;
     }
 
+    const bool overlap = p.overlap != 0;
     int64_t ctas;
     bool combine;
     if (plan.dense) {
@@ -1170,8 +1212,8 @@ int spk_attn_stream_launch(const AttnParams& p, const StreamPlan& plan, int head
     }
     if (ctas > 0x7fffffffLL) return SPK_ERR_TOO_LARGE;
     int rc;
-    if (head_dim == 64) rc = wide ? launch_stream<2, 2>(p, sp, ctas, stream) : launch_stream<2, 1>(p, sp, ctas, stream);
-    else rc = wide ? launch_stream<4, 2>(p, sp, ctas, stream) : launch_stream<4, 1>(p, sp, ctas, stream);
+    if (head_dim == 64) rc = wide ? launch_stream<2, 2>(p, sp, ctas, overlap, stream) : launch_stream<2, 1>(p, sp, ctas, overlap, stream);
+    else rc = wide ? launch_stream<4, 2>(p, sp, ctas, overlap, stream) : launch_stream<4, 1>(p, sp, ctas, overlap, stream);
     if (rc != SPK_OK) return rc;
     return combine ? launch_combine(p, sp, head_dim, stream) : SPK_OK;
 }

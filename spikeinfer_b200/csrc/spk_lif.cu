@@ -620,6 +620,9 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
 template <int MODE, bool ROPE, bool FULL, bool ASYNC, bool PLAIN>
 __global__ void __launch_bounds__(kFusedThreads, ROPE ? 1 : (ASYNC ? 4 : 2))
 lif_pack_scatter_vec_kernel(VecArgs args, int T, int64_t n_tok, uint32_t* status) {
+    // A next launch that asked to overlap this one (the attention after the q/k/v sites: it reads only lengths and
+    // block tables until this grid has finished) may be placed from now on; without such a launch this does nothing.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ uint4 stage_smem[];
     const int site = blockIdx.y;
     const int lane = threadIdx.x & 31;
@@ -767,6 +770,7 @@ __device__ __forceinline__ void fused_site(const spk_lif_site& s, int groups, in
 template <int MODE>
 __global__ void __launch_bounds__(kFusedThreads)
 lif_pack_scatter_kernel(SiteArgs args, int T, int64_t n_tok, uint32_t* status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // see lif_pack_scatter_vec_kernel
     const int site = blockIdx.y;
     const int lane = threadIdx.x & 31;
     const int64_t warp = (static_cast<int64_t>(blockIdx.x) * kFusedThreads + threadIdx.x) >> 5;

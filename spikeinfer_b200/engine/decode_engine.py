@@ -37,7 +37,8 @@ class SpikeDecodeEngine:
         self.ledger = BlockLedger(num_blocks - 1, block_size, self.max_blocks)  # host count of the device free list
         self.meta = AttentionMetadata(
             slot_mapping=self.state.slot_mapping, block_size=block_size, num_decode_tokens=max_num_seqs,
-            block_tables=self.state.block_tables, seq_lens=self.state.seq_lens, status=self.state.status)
+            block_tables=self.state.block_tables, seq_lens=self.state.seq_lens, status=self.state.status,
+            tables_settled=True)  # written by the metadata kernel at the head of the step, layers before any attention
         self.use_graph = use_graph
         # True: prompts attend through the packed popcount kernel in one batched launch per layer (3x faster at
         # 64 prompts of 128 tokens, exact-score fp32 softmax).  False (default): one SDPA per sequence on unpacked

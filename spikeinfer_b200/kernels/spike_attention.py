@@ -43,6 +43,7 @@ def paged_spike_attn_decode(
     out: torch.Tensor | None = None,
     dtype: torch.dtype = torch.float32,
     status: torch.Tensor | None = None,
+    overlap_previous: bool = False,
 ) -> torch.Tensor:
     """One decode step of attention against the paged spike cache.
 
@@ -50,7 +51,9 @@ def paged_spike_attn_decode(
     views allowed); block_tables ``int32 [N, max_blocks]``; seq_lens ``int32 [N]`` including the token
     being decoded.  ``out`` (optional, may be a strided view such as ``buf[:, :n_dec]``) receives
     ``[T, N, H_q, head_dim]``; its dtype decides the output type.  Launches on the current stream,
-    never synchronises.
+    never synchronises.  ``overlap_previous=True`` lets the launch overlap the kernel before it on the
+    stream (it then reads only ``block_tables`` and ``seq_lens`` until that kernel has finished): pass it only
+    when those two were complete before that kernel began.
     """
     T, n_seqs, n_heads, words = q_packed.shape
     if words != packed_width(head_dim):
@@ -80,6 +83,8 @@ def paged_spike_attn_decode(
                                                    block_size, max_blocks)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes > 0 else None
     with torch.cuda.device(dev):
+        if overlap_previous:
+            lib.spk_attn_overlap_next_call()
         rc = lib.spk_attn_decode(
             q_packed.data_ptr(), q_packed.stride(0), q_packed.stride(1), q_packed.stride(2),
             k_cache.data_ptr(), sk[0], sk[1], sk[2], sk[3],

@@ -64,6 +64,10 @@ def test_host_side_argument_checks(lib):
     record = (8 * 64 + 8) * 4                    # eight heads x 64 sums + 8 totals, fp32
     assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 1) == 0
     assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 16) == 0
+    # tables of up to 768 keys are never cut (one warp walks such a row faster than a combine pass would cost)
+    # (what is left at 48 pages are the two 512-key unit records per item of the selectable tcgen05 form)
+    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 48) == 64 * 4 * 2 * 2 * record
+    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 49) == (64 * 4 * 2 * 25 // 8) * 2 * record + 65 * 4
     assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 256) == 148 * 20 * 2 * record + 65 * 4
     ws = lib.spk_attn_decode_workspace_bytes(4, 8, 14, 2, 64, 16, 256)
     assert ws == (8 * 4 * 2 * 128 // 8) * 2 * record + 9 * 4

@@ -205,6 +205,39 @@ def test_config2_full_size(dev):
     assert torch.equal(kernels.qk_scores(**to_dev(sub, dev)).cpu(), orc.qk_scores(**sub))
 
 
+def test_launches_that_overlap_their_predecessor_give_the_same_results(dev):
+    """overlap_previous lets a call's prologue run under the launch before it (here: the previous call's combine
+    pass, and a kernel that rewrites q).  Lengths and tables are fixed, everything else changes from call to call:
+    q is produced by the kernel just before each call, pools and outputs alternate, and the calls share one
+    workspace address (the caching allocator hands the same block back).  Every result must equal the one the
+    ordinary launch gives, bit for bit."""
+    specs = [dict(seq_lens=[700, 130, 1, 1500, 64, 2047], max_blocks=128, seed=41),
+             dict(seq_lens=[700, 130, 1, 1500, 64, 2047], max_blocks=128, seed=42, density=0.4)]
+    data = [to_dev(cases.attention_case(**s), dev) for s in specs]
+    for d in data:
+        d["block_tables"], d["seq_lens"] = data[0]["block_tables"], data[0]["seq_lens"]
+    want = [kernels.paged_spike_attn_decode(**d) for d in data]
+    want16 = [kernels.paged_spike_attn_decode(**d, dtype=torch.bfloat16) for d in data]
+    torch.cuda.synchronize(dev)
+    for rounds in range(3):
+        outs, outs16 = [], []
+        for i in range(6):
+            d = dict(data[i % 2])
+            d["q_packed"] = d["q_packed"] | 0  # q comes out of the kernel launched just before the attention
+            outs.append(kernels.paged_spike_attn_decode(**d, overlap_previous=True))
+            d["q_packed"] = d["q_packed"] | 0
+            outs16.append(kernels.paged_spike_attn_decode(**d, dtype=torch.bfloat16, overlap_previous=True))
+        for i in range(6):
+            assert torch.equal(outs[i], want[i % 2]) and torch.equal(outs16[i], want16[i % 2])
+    # a short batch (no row is cut, no combine pass) behind a kernel that writes q
+    short = to_dev(cases.attention_case(seq_lens=[5, 130, 200, 17], max_blocks=16, seed=43), dev)
+    ref = kernels.paged_spike_attn_decode(**short)
+    for _ in range(4):
+        d = dict(short)
+        d["q_packed"] = d["q_packed"] | 0
+        assert torch.equal(kernels.paged_spike_attn_decode(**d, overlap_previous=True), ref)
+
+
 def test_general_form_still_serves_every_layout(dev, lib):
     """With the streaming form switched off, the general form takes the same calls (it is what small pages, odd
     strides and head_dim 32 / 96 use): the kernel-level attention configuration against the oracle."""
