@@ -241,8 +241,9 @@ def closed_loop(model, cfg, device, concurrency: int, n_requests: int, k: int = 
     """The reference's closed-loop protocol (spikeinfer/bench.py:29-116): `concurrency` requests in flight, each
     replaced by the next one as soon as it finishes, 128 prompt tokens in, 64 greedy tokens out.  Everything is
     inside the clock: prefill (groups of up to 16 prompts), admission, the host visit that reads the tokens (one
-    per k decode steps; the reference visits every step), release.  The decode graph is captured for exactly
-    `concurrency` rows (the reference keeps one graph per batch-size bucket)."""
+    per k decode steps; the reference visits every step), release.  The engine holds `concurrency` rows and one
+    decode graph per bucket of rows up to that (as the reference does); a step replays the smallest bucket that
+    covers the batch."""
     from spikeinfer_b200.engine.decode_engine import SpikeDecodeEngine
 
     max_len = -(-(PROMPT_LEN + OUT_LEN + BLOCK_SIZE) // BLOCK_SIZE) * BLOCK_SIZE
@@ -253,7 +254,7 @@ def closed_loop(model, cfg, device, concurrency: int, n_requests: int, k: int = 
     sync = lambda: torch.cuda.synchronize(device)
     # warm-up, as the reference does (two requests): prefill kernels, graph capture
     rows = engine.add_requests(prompts[-2:][:min(2, concurrency)])
-    engine.capture()
+    engine.capture_all()
     engine.decode_steps(2)
     for r in rows:
         engine.release(r)
@@ -309,7 +310,7 @@ def open_loop(model, cfg, device, rate: float = 8.0, n_requests: int = 64, seed:
     arrivals = torch.cumsum(torch.empty(n_requests).exponential_(rate, generator=g), 0).tolist()
     sync = lambda: torch.cuda.synchronize(device)
     rows = engine.add_requests(prompts[-1:])
-    engine.capture()
+    engine.capture_all()  # one graph per bucket of rows (1, 2, 4, ... 64): a step replays the smallest that covers the batch
     engine.decode_steps(2)
     engine.release(rows[0])
     sync()
@@ -356,6 +357,7 @@ ATTN_KERNEL = "attn_stream_kernel<W=2,NB=1,dense>"  # what bf16 output at head_d
 
 
 ATTN_OVERLAP = False  # --attn-overlap sets it
+ATTN_PAGE_MAJOR = False  # --attn-page-major sets it
 
 
 def time_attention(device, lens, max_blocks, n_pools, iters, repeats, hd=64, hq=14, hkv=2) -> dict:
@@ -370,7 +372,18 @@ def time_attention(device, lens, max_blocks, n_pools, iters, repeats, hd=64, hq=
     case = cases.attention_case(seq_lens=lens, density=0.2, seed=2, spare_blocks=0, max_blocks=max_blocks,
                                 head_dim=hd, num_q_heads=hq, num_kv_heads=hkv)
     d = {k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
-    pools = [(d["k_cache"].clone(), d["v_cache"].clone()) for _ in range(n_pools)]
+    if ATTN_PAGE_MAJOR:
+        # one buffer [block, T, H_kv, K|V, slot, W] (a page's 2 KB contiguous); K and V as strided 5-D views of it
+        def page_major(k, v):
+            T_, H_, slots_, W_ = k.shape
+            nb = slots_ // BLOCK_SIZE
+            buf = torch.empty((nb, T_, H_, 2, BLOCK_SIZE, W_), dtype=k.dtype, device=device)
+            buf[:, :, :, 0] = k.view(T_, H_, nb, BLOCK_SIZE, W_).permute(2, 0, 1, 3, 4)
+            buf[:, :, :, 1] = v.view(T_, H_, nb, BLOCK_SIZE, W_).permute(2, 0, 1, 3, 4)
+            return buf[:, :, :, 0].permute(1, 2, 0, 3, 4), buf[:, :, :, 1].permute(1, 2, 0, 3, 4)
+        pools = [page_major(d["k_cache"], d["v_cache"]) for _ in range(n_pools)]
+    else:
+        pools = [(d["k_cache"].clone(), d["v_cache"].clone()) for _ in range(n_pools)]
     out = torch.empty(4, len(lens), hq, hd, dtype=torch.bfloat16, device=device)
 
     def run_all():
@@ -404,7 +417,7 @@ def time_attention(device, lens, max_blocks, n_pools, iters, repeats, hd=64, hq=
     med = statistics.median(us)
     return {"us_per_call": stats(us, 2), "algorithmic_bytes": alg, "achieved_GBs": round(alg / med / 1e3, 1),
             "frac": round(alg / med / 1e3 / peak, 4), "pools": n_pools, "sum_keys": sum(lens),
-            "overlaps_previous_call": ATTN_OVERLAP}
+            "overlaps_previous_call": ATTN_OVERLAP, "pool_layout": "page_major" if ATTN_PAGE_MAJOR else "reference"}
 
 
 def attention_roofline(device, n_pools: int = 24, iters: int = 10, repeats: int = 5, extra: bool = True,
@@ -919,6 +932,8 @@ def main() -> None:
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--kernel-bench", choices=["attn", "lif"], default=None,
                     help="time only the kernel-level configuration of the attention or the LIF kernel")
+    ap.add_argument("--attn-page-major", action="store_true",
+                    help="kernel-level attention timing on the page-major pool layout [block, T, H_kv, K|V, slot, W]")
     ap.add_argument("--attn-overlap", action="store_true",
                     help="kernel-level attention timing with programmatic dependent launch between calls")
     ap.add_argument("--attn-form", choices=["auto", "general", "tcgen05"], default="auto",
@@ -936,9 +951,8 @@ def main() -> None:
     ap.add_argument("--tp-layers", type=int, default=0, help="layers of --workload tp7b (default 28)")
     ap.add_argument("--verbose", action="store_true", help="print progress of the set-up stages to stderr")
     args = ap.parse_args()
-    if args.attn_overlap:
-        global ATTN_OVERLAP
-        ATTN_OVERLAP = True
+    global ATTN_OVERLAP, ATTN_PAGE_MAJOR
+    ATTN_OVERLAP, ATTN_PAGE_MAJOR = args.attn_overlap, args.attn_page_major
     if args.workload == "tp7b" and args.impl == "own" and not args.kernel_bench:
         run_tp7b(args)
     elif args.kernel_bench:

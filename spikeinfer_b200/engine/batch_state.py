@@ -52,14 +52,18 @@ class DecodeBatchState:
         self.next_tokens.zero_()
         self.status.zero_()
 
-    def advance(self) -> None:
-        """One decode step for every active row (graph-capturable: no host-dependent argument)."""
+    def advance(self, rows: int | None = None) -> None:
+        """One decode step for every active row among the first ``rows`` (default: all rows).  Graph-capturable:
+        no host-dependent argument.  Rows beyond ``rows`` must be inactive."""
+        rows = self.max_rows if rows is None else rows
+        if not 0 < rows <= self.max_rows:
+            raise ValueError(f"rows must be in 1..{self.max_rows}")
         with torch.cuda.device(self.device):
             rc = self._lib.spk_meta_advance(
                 self.free_list.data_ptr(), self._free_count.data_ptr(), self.active.data_ptr(),
                 self.seq_lens.data_ptr(), self.positions.data_ptr(), self.slot_mapping.data_ptr(),
                 self.block_tables.data_ptr(), self.input_ids.data_ptr(), self.next_tokens.data_ptr(),
-                self.max_rows, self.max_blocks, self.pad_block, self.block_size, self.status.data_ptr(),
+                rows, self.max_blocks, self.pad_block, self.block_size, self.status.data_ptr(),
                 self._stream())
         _lib.check(rc, "spk_meta_advance")
 

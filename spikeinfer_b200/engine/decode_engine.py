@@ -4,7 +4,10 @@ Plays the role of ``ModelRunner`` + ``CUDAGraphRunner`` of the reference
 (``spikeinfer/engine/model_runner.py:143-215``, ``:218-287``) for the decode path, with two
 differences: the per-step metadata is advanced on the GPU by ``DecodeBatchState.advance`` inside the
 captured graph (no host-built tensors, no buffer copies at replay), and greedy sampling (argmax) is
-captured too, so a step is a single graph launch that feeds itself.  ``step_host`` is the
+captured too, so a step is a single graph launch that feeds itself.  Like the reference
+(``model_runner.py:143-182``, ``config.py:118-126``) a step replays the smallest captured bucket of rows
+that covers the batch: rows are handed out lowest first, a bucket of b rows runs rows 0..b-1, and a bucket
+is captured the first time it is needed.  ``step_host`` is the
 host-in-the-loop form (tokens cross PCIe both ways every step, as in the reference engine, which needs
 them for detokenisation and stop checks).
 """
@@ -22,7 +25,8 @@ from .spike_cache import PagedSpikeCache
 
 class SpikeDecodeEngine:
     def __init__(self, model: SpikingQwenModel, num_blocks: int, block_size: int = 16, max_num_seqs: int = 64,
-                 max_model_len: int = 4096, use_graph: bool = True, packed_prefill: bool = False) -> None:
+                 max_model_len: int = 4096, use_graph: bool = True, packed_prefill: bool = False,
+                 graph_buckets: bool = True) -> None:
         c = model.config
         self.model = model
         self.device = model.device
@@ -35,17 +39,16 @@ class SpikeDecodeEngine:
                                      block_size, device=self.device)
         self.state = DecodeBatchState(max_num_seqs, self.max_blocks, num_blocks, block_size, device=self.device)
         self.ledger = BlockLedger(num_blocks - 1, block_size, self.max_blocks)  # host count of the device free list
-        self.meta = AttentionMetadata(
-            slot_mapping=self.state.slot_mapping, block_size=block_size, num_decode_tokens=max_num_seqs,
-            block_tables=self.state.block_tables, seq_lens=self.state.seq_lens, status=self.state.status,
-            tables_settled=True)  # written by the metadata kernel at the head of the step, layers before any attention
         self.use_graph = use_graph
+        # row counts a step can run on: powers of two up to max_num_seqs, and max_num_seqs itself
+        self.buckets = sorted({min(1 << i, max_num_seqs) for i in range(max_num_seqs.bit_length() + 1)}) \
+            if graph_buckets else [max_num_seqs]
+        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         # True: prompts attend through the packed popcount kernel in one batched launch per layer (3x faster at
         # 64 prompts of 128 tokens, exact-score fp32 softmax).  False (default): one SDPA per sequence on unpacked
         # spikes in the model dtype, as the reference does; in bf16 that rounds the probabilities to bf16, so
         # the two differ at the 1e-2 level there, enough to flip near-tie tokens.  In fp32 they agree to 1e-5.
         self.packed_prefill = packed_prefill
-        self.graph: torch.cuda.CUDAGraph | None = None
         self.free_rows = list(range(max_num_seqs - 1, -1, -1))
         self.host_in = torch.zeros(max_num_seqs, dtype=torch.int64).pin_memory()
         self.host_out = torch.zeros(max_num_seqs, dtype=torch.int64).pin_memory()
@@ -101,6 +104,7 @@ class SpikeDecodeEngine:
         self.state.release(row)
         self.ledger.release(row)
         self.free_rows.append(row)
+        self.free_rows.sort(reverse=True)  # lowest row first out: the batch stays within the smallest bucket
 
     # -- snapshots (benchmarks and tests: repeat the same steps from the same state) ---------------------
     def _state_tensors(self):
@@ -122,17 +126,51 @@ class SpikeDecodeEngine:
         self.free_rows = list(snap["free_rows"])
 
     # -- decode -----------------------------------------------------------
-    def _body(self) -> None:
+    def _meta(self, rows: int) -> AttentionMetadata:
         st = self.state
-        st.advance()
-        hidden = self.model.forward_paged(st.input_ids, st.positions, self.cache.layers, self.meta)
+        # tables and lengths are written by the metadata kernel at the head of the step, layers before any attention
+        return AttentionMetadata(
+            slot_mapping=st.slot_mapping[:rows], block_size=self.block_size, num_decode_tokens=rows,
+            block_tables=st.block_tables[:rows], seq_lens=st.seq_lens[:rows], status=st.status, tables_settled=True)
+
+    @property
+    def meta(self) -> AttentionMetadata:
+        """Decode metadata over all rows."""
+        return self._meta(self.max_num_seqs)
+
+    def _body(self, rows: int | None = None) -> None:
+        st = self.state
+        rows = self.max_num_seqs if rows is None else rows
+        st.advance(rows)
+        hidden = self.model.forward_paged(st.input_ids[:rows], st.positions[:rows], self.cache.layers, self._meta(rows))
         logits = self.model.compute_logits(hidden)
-        argmax_rows(logits, out=st.next_tokens, workspace=self.sample_ws)  # greedy, inside the graph
+        argmax_rows(logits, out=st.next_tokens[:rows], workspace=self.sample_ws)  # greedy, inside the graph
+
+    def bucket_for_batch(self) -> int:
+        """Smallest bucket that covers every admitted row (rows are handed out lowest first)."""
+        top = max(self.ledger.seq_lens, default=-1) + 1
+        for b in self.buckets:
+            if b >= top:
+                return b
+        return self.max_num_seqs
+
+    @property
+    def graph(self) -> torch.cuda.CUDAGraph | None:
+        """The captured step over all rows (None before capture)."""
+        return self.graphs.get(self.max_num_seqs)
+
+    @graph.setter
+    def graph(self, value) -> None:
+        if value is not None:
+            raise ValueError("assign None to drop the captured graphs")
+        self.graphs.clear()
 
     @torch.no_grad()
-    def capture(self) -> None:
-        """Capture one decode step.  Warm-up runs would advance real rows, so capture happens on a
-        snapshot of the batch state and pools' pad block only: the state is saved and restored."""
+    def capture(self, rows: int | None = None) -> None:
+        """Capture one decode step over ``rows`` rows (default: all).  Warm-up runs would advance real rows, so
+        capture happens on a snapshot of the batch state and the pools' pad block only: the state is saved and
+        restored.  All buckets share one memory pool (they never run at the same time)."""
+        rows = self.max_num_seqs if rows is None else rows
         st = self.state
         saved = [t.clone() for t in self._state_tensors()]
         active = st.active.clone()
@@ -141,25 +179,34 @@ class SpikeDecodeEngine:
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
             for _ in range(3):
-                self._body()
+                self._body(rows)
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self._body()
+        graph = torch.cuda.CUDAGraph()
+        pool = next(iter(self.graphs.values())).pool() if self.graphs else None
+        with torch.cuda.graph(graph, pool=pool):
+            self._body(rows)
+        self.graphs[rows] = graph
         for t, s in zip(self._state_tensors(), saved):
             t.copy_(s)
         st.active.copy_(active)
 
+    def capture_all(self) -> None:
+        """Capture every bucket now (largest first, so that the shared pool is sized once) instead of on first use."""
+        for b in sorted(self.buckets, reverse=True):
+            if b not in self.graphs:
+                self.capture(b)
+
     @torch.no_grad()
     def decode_step(self) -> None:
         """One token for every active row; tokens stay on the device (``state.next_tokens``)."""
+        rows = self.bucket_for_batch()
         if self.use_graph:
-            if self.graph is None:
-                self.capture()
-            self.graph.replay()
+            if rows not in self.graphs:
+                self.capture(rows)
+            self.graphs[rows].replay()
         else:
-            self._body()
+            self._body(rows)
         self.ledger.advance()
 
     @torch.no_grad()

@@ -183,6 +183,46 @@ def test_engine_tokens_match_reference(variant, use_graph, packed_prefill, dev, 
     assert worst <= POOL_DIFF_BOUND, f"{worst:.2e} of a layer's cached bits differ from the CPU run"
 
 
+def test_bucket_graphs_follow_the_batch(dev, golden):
+    """A step replays the smallest captured bucket that covers the admitted rows (rows are handed out lowest first);
+    through admissions and releases the tokens equal those of an engine that always runs all rows."""
+    g, shape, w = build(golden, "random_lif")
+    model = SpikingQwenModel(SpikingQwenConfig(**g["config"]), w, device=dev)
+    prompts = tiny_prompts(shape.vocab_size)
+    logs = []
+    for buckets in (True, False):
+        eng = SpikeDecodeEngine(model, g["num_blocks"], g["block_size"], max_num_seqs=8, max_model_len=g["max_len"],
+                                graph_buckets=buckets)
+        assert eng.buckets == ([1, 2, 4, 8] if buckets else [8])
+        log, used = [], []
+
+        def run(n_steps, rows):
+            for _ in range(n_steps):
+                used.append(eng.bucket_for_batch())
+                eng.decode_step()
+                log.append([int(eng.state.next_tokens[r]) for r in rows])
+
+        rows = eng.add_requests(prompts)
+        run(3, [0, 1, 2, 3])
+        eng.release(3)
+        eng.release(2)
+        run(2, [0, 1])
+        eng.release(1)
+        run(2, [0])
+        assert eng.add_requests([prompts[3]]) == [1]  # the lowest free row
+        run(2, [0, 1])
+        assert eng.add_requests([prompts[2], prompts[1]]) == [2, 3]
+        run(2, [0, 1, 2, 3])
+        eng.state.check_status()
+        if buckets:
+            assert used == [4] * 3 + [2] * 2 + [1] * 2 + [2] * 2 + [4] * 2
+            assert sorted(eng.graphs) == [1, 2, 4]
+        else:
+            assert set(used) == {8} and sorted(eng.graphs) == [8]
+        logs.append(log)
+    assert logs[0] == logs[1]
+
+
 def test_admission_control_and_block_ledger(dev, golden):
     """Over-admission raises before anything is taken from the device list and leaves pools, tables and the free
     list untouched; the host ledger's free count equals the device's after prefill, decode steps and a release."""
