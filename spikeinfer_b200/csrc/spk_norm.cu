@@ -78,6 +78,13 @@ add_rmsnorm_row_kernel(T* __restrict__ h, const T* __restrict__ delta, const T* 
     T* hr = h + row * hidden;
     const T* dr = delta != nullptr ? delta + row * hidden : nullptr;
     const int n_vec = hidden / E;
+    // the norm weights: in flight together with the row
+    uint4 wraw[kVecPerThread];
+#pragma unroll
+    for (int k = 0; k < kVecPerThread; ++k) {
+        const int i = threadIdx.x + k * kRowThreads;
+        wraw[k] = i < n_vec ? __ldg(reinterpret_cast<const uint4*>(weight + i * E)) : make_uint4(0, 0, 0, 0);
+    }
     float v[kVecPerThread][E];
     float ss = 0.0f;
 #pragma unroll
@@ -115,8 +122,7 @@ add_rmsnorm_row_kernel(T* __restrict__ h, const T* __restrict__ delta, const T* 
     for (int k = 0; k < kVecPerThread; ++k) {
         const int i = threadIdx.x + k * kRowThreads;
         if (i < n_vec) {
-            const uint4 wraw = __ldg(reinterpret_cast<const uint4*>(weight + i * E));
-            const T* we = reinterpret_cast<const T*>(&wraw);
+            const T* we = reinterpret_cast<const T*>(&wraw[k]);
             uint4 oraw;
             T* oe = reinterpret_cast<T*>(&oraw);
 #pragma unroll
