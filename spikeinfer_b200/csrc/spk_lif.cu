@@ -550,6 +550,39 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
                 if (sub == i) mine = word;
             }
             if (wp != nullptr && (FULL || sub < T)) *wp = mine;
+        } else if (PLAIN && FULL) {
+            // The same channel-major form for launches too small to stream: the four timesteps straight from global
+            // memory (four independent 16-byte loads per lane), T a multiple of four.
+            for (int t0 = 0; t0 < T; t0 += kStepGroup) {
+                Raw8<TX> raw[kStepGroup];
+#pragma unroll
+                for (int i = 0; i < kStepGroup; ++i) raw[i].load(xp + i * sx_t);
+                uint32_t bits[kStepGroup] = {0, 0, 0, 0};
+                if (t0 == 0) {
+                    float uf[kSeg];
+                    chain8<MODE, TX>(raw, b, th, uf, bits, std::make_integer_sequence<int, kSeg>{});
+                    // membrane after the fourth step; its pending reset (u > th) is what init derives
+#pragma unroll
+                    for (int c = 0; c < kSeg; ++c) st[c].init(uf[c], th[c]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < kStepGroup; ++i)
+                        step8<MODE, TX>(st, raw[i], b, th, bits[i], std::make_integer_sequence<int, kSeg>{});
+                }
+                uint32_t mine = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+                if (all_live) {
+                    mine = __byte_perm(mine, __shfl_xor_sync(0xffffffffu, mine, 1), sel_a);
+                    mine = __byte_perm(mine, __shfl_xor_sync(0xffffffffu, mine, 2), sel_b);
+                } else {
+                    mine = __byte_perm(mine, __shfl_xor_sync(group_mask, mine, 1), sel_a);
+                    mine = __byte_perm(mine, __shfl_xor_sync(group_mask, mine, 2), sel_b);
+                }
+                if (wp != nullptr) {
+                    *wp = mine;
+                    wp += kStepGroup * so_t;
+                }
+                xp += kStepGroup * sx_t;
+            }
         } else
         for (int t0 = 0; t0 < T; t0 += kStepGroup) {
             Raw8<TX> raw[kStepGroup], partner[kStepGroup], mulv[kStepGroup];
@@ -932,6 +965,7 @@ extern "C" int spk_lif_pack_scatter(const spk_lif_site* sites, int n_sites, int 
         if (streaming && full && plain) SPK_LAUNCH_VEC(MODE_, false, true, true, true); \
         else if (streaming) { if (full) SPK_LAUNCH_VEC(MODE_, false, true, true, false); else SPK_LAUNCH_VEC(MODE_, false, false, true, false); } \
         else if (any_rope) { if (full) SPK_LAUNCH_VEC(MODE_, true, true, false, false); else SPK_LAUNCH_VEC(MODE_, true, false, false, false); } \
+        else if (full && plain) SPK_LAUNCH_VEC(MODE_, false, true, false, true); \
         else { if (full) SPK_LAUNCH_VEC(MODE_, false, true, false, false); else SPK_LAUNCH_VEC(MODE_, false, false, false, false); } \
     } while (0)
             if (sub) SPK_LAUNCH_MODE(SPK_RESET_SUBTRACT_DELAYED);

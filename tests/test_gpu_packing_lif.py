@@ -257,6 +257,34 @@ def test_config3_full_size_gate_and_kv(reset_mode, dev):
         assert torch.equal(pool.cpu(), want)
 
 
+@pytest.mark.parametrize("reset_mode", [orc.SUBTRACT_DELAYED, orc.HARD_ZERO], ids=["subtract_delayed", "hard_zero"])
+def test_streaming_form_edges(reset_mode, dev):
+    """The bandwidth-sized (streaming, channel-major) form away from the comfortable case: a token count that leaves
+    a ragged last group (5003 = 625 x 8 + 3), thresholds that are negative, zero and positive (a negative threshold
+    makes the zero membrane spike before the first step), decay factors 0, 1 and out of range (clamped), currents
+    that hold exact zeros of both signs and values that land on the threshold; with and without the membrane."""
+    T, n_tok, N = 4, 5003, 4864
+    g = cases.gen(33)
+    th = torch.rand(N, generator=g) * 2.0 - 0.5
+    th[::97] = 0.0
+    th[1::97] = -0.25
+    beta = torch.rand(N, generator=g)
+    beta[::53], beta[1::53], beta[2::53], beta[3::53] = 0.0, 1.0, 1.5, -0.5
+    x = torch.randn(T, n_tok, N, generator=g)
+    x[:, ::7, ::5] = 0.0
+    x[:, 1::7, ::5] = -0.0
+    x[0, 2::7] = th  # lands exactly on the threshold at the first step: no spike
+    x = x.to(torch.bfloat16)
+    want_s, want_u = orc.lif_multistep(x, beta, th, out_dtype=torch.uint8, reset_mode=reset_mode)
+    want_p = orc.pack_spikes(want_s)
+    d = x.to(dev)
+    packed, _, mem = kernels.lif_pack(d, beta.to(dev), th.to(dev), return_membrane=True, reset_mode=reset_mode)
+    assert torch.equal(packed.cpu(), want_p) and torch.equal(mem.cpu(), want_u)
+    packed2, _, _ = kernels.lif_pack(d, beta.to(dev), th.to(dev), reset_mode=reset_mode)
+    assert torch.equal(packed2.cpu(), want_p)
+    assert 0.05 < want_s.float().mean().item() < 0.95
+
+
 # ------------------------------------------------------------------ fused RoPE, gated product, add + RMSNorm
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_fused_rope_is_bit_exact_with_the_eager_expression(dtype, dev):
