@@ -69,3 +69,21 @@ class BlockLedger:
     def release(self, row: int) -> None:
         n = self.seq_lens.pop(row)
         self.free += min(self.blocks_for(n), self.max_blocks_per_seq)
+
+
+def row_buckets(max_rows: int) -> list[int]:
+    """Row counts a decode step can be captured for: the powers of two up to ``max_rows``, and ``max_rows``
+    itself (the reference keeps such a list of batch-size buckets, ``spikeinfer/config.py:118-126``)."""
+    if max_rows < 1:
+        raise ValueError("max_rows must be at least 1")
+    return sorted({min(1 << i, max_rows) for i in range(max_rows.bit_length() + 1)})
+
+
+def covering_bucket(buckets: list[int], rows_in_use) -> int:
+    """Smallest bucket that covers every row in use (rows are handed out lowest first, so a bucket of b rows
+    runs rows 0..b-1); the largest bucket when none does."""
+    top = max(rows_in_use, default=-1) + 1
+    for b in buckets:
+        if b >= top:
+            return b
+    return buckets[-1]

@@ -19,7 +19,7 @@ from ..attention import AttentionMetadata, build_prefill_rows
 from ..kernels import argmax_rows, argmax_workspace_bytes
 from ..modeling import SpikingQwenModel
 from .batch_state import DecodeBatchState
-from .block_ledger import BlockLedger
+from .block_ledger import BlockLedger, covering_bucket, row_buckets
 from .spike_cache import PagedSpikeCache
 
 
@@ -41,8 +41,7 @@ class SpikeDecodeEngine:
         self.ledger = BlockLedger(num_blocks - 1, block_size, self.max_blocks)  # host count of the device free list
         self.use_graph = use_graph
         # row counts a step can run on: powers of two up to max_num_seqs, and max_num_seqs itself
-        self.buckets = sorted({min(1 << i, max_num_seqs) for i in range(max_num_seqs.bit_length() + 1)}) \
-            if graph_buckets else [max_num_seqs]
+        self.buckets = row_buckets(max_num_seqs) if graph_buckets else [max_num_seqs]
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         # True: prompts attend through the packed popcount kernel in one batched launch per layer (3x faster at
         # 64 prompts of 128 tokens, exact-score fp32 softmax).  False (default): one SDPA per sequence on unpacked
@@ -148,11 +147,7 @@ class SpikeDecodeEngine:
 
     def bucket_for_batch(self) -> int:
         """Smallest bucket that covers every admitted row (rows are handed out lowest first)."""
-        top = max(self.ledger.seq_lens, default=-1) + 1
-        for b in self.buckets:
-            if b >= top:
-                return b
-        return self.max_num_seqs
+        return covering_bucket(self.buckets, self.ledger.seq_lens)
 
     @property
     def graph(self) -> torch.cuda.CUDAGraph | None:

@@ -140,3 +140,22 @@ def test_block_ledger_counts_follow_the_allocation_rules():
     led2.admit(3, 2)
     led2.advance()
     assert led2.seq_lens[3] == 2 and led2.free == 0
+
+
+def test_row_buckets_and_the_covering_bucket():
+    from spikeinfer_b200.engine.block_ledger import covering_bucket, row_buckets
+
+    assert row_buckets(1) == [1]
+    assert row_buckets(8) == [1, 2, 4, 8]
+    assert row_buckets(48) == [1, 2, 4, 8, 16, 32, 48]
+    assert row_buckets(64) == [1, 2, 4, 8, 16, 32, 64]
+    b = row_buckets(48)
+    assert covering_bucket(b, []) == 1                  # an idle engine runs the smallest graph
+    assert covering_bucket(b, [0]) == 1
+    assert covering_bucket(b, [0, 1]) == 2
+    assert covering_bucket(b, [5]) == 8                 # the highest row in use decides, not the count
+    assert covering_bucket(b, {0: 10, 32: 7}) == 48     # dict of row -> length, as the ledger keeps it
+    assert covering_bucket(b, range(48)) == 48
+    assert covering_bucket([48], [0]) == 48             # buckets switched off
+    with pytest.raises(ValueError):
+        row_buckets(0)
