@@ -1114,6 +1114,12 @@ StreamPlan spk_attn_stream_plan(int T, int64_t n_seqs, int Hq, int Hkv, int head
         pl.workers = workers;
         pl.short_steps = max_steps <= kUncutSteps ? static_cast<int>(max_steps) : kShortSteps;
         pl.cut = max_steps > pl.short_steps;
+        if (!pl.cut) {
+            // whole items only: a warp per item while the GPU holds them all at once
+            const int64_t items = n_seqs * gt;
+            if (workers < items) workers = items < cap ? items : cap;
+            pl.workers = workers;
+        }
         if (pl.cut) range_bytes = ((workers * 2 * rec_bytes + 15) / 16) * 16 + (n_seqs + 1) * static_cast<int64_t>(sizeof(int));
     }
     // the tcgen05 form (selectable at head_dim 64) uses the unit records
@@ -1205,6 +1211,15 @@ int spk_attn_stream_launch(const AttnParams& p, const StreamPlan& plan, int head
                                  : nullptr;
         ctas = (sp.workers + kWarps - 1) / kWarps;
         combine = plan.cut;
+        if (!plan.cut && sp.workers >= p.n_seqs * sp.gt) {
+            // Nothing can be cut and the GPU holds a warp per item at once: warp w runs item w whole, whatever the
+            // rows' lengths (equal step ranges would hand some warps two ragged items and others none).  That is
+            // the unit form with one unit per row, which also needs no step prefix.
+            sp.dense = 0;
+            sp.unit_log2 = 30;
+            sp.max_units = 1;
+            ctas = (p.n_seqs * sp.gt + kWarps - 1) / kWarps;
+        }
     } else {
         // worst case of the enumeration: every row of max_units units (the surplus warps leave at once)
         ctas = (p.n_seqs * plan.max_units * sp.gt + kWarps - 1) / kWarps;

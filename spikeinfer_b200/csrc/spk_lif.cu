@@ -285,6 +285,14 @@ __device__ __forceinline__ void chain8(const Raw8<TX> (&raw)[4], const float (&b
                                           bits[0], bits[1], bits[2], bits[3])), ...);
 }
 
+// The same with the currents supplied by `cur(t, channel)` (e.g. rotated on the fly).
+template <int MODE, typename F, int... C>
+__device__ __forceinline__ void chain8_of(F&& cur, const float (&b)[8], const float (&th)[8], float (&u)[8],
+                                          uint32_t (&bits)[4], std::integer_sequence<int, C...>) {
+    ((u[C] = lif_chain4<MODE, (1u << C)>(cur(0, C), cur(1, C), cur(2, C), cur(3, C), b[C], th[C], bits[0], bits[1],
+                                          bits[2], bits[3])), ...);
+}
+
 // One timestep of the 8 channels of a segment; bit c of `bits` = spike of channel c.
 template <int MODE, typename TX, int... C>
 __device__ __forceinline__ void step8(Lif (&st)[8], const Raw8<TX>& raw, const float (&b)[8], const float (&th)[8],
@@ -406,7 +414,7 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
     }
     const int sub = lane & 3;  // position of this lane's byte within its word
     // rotary embedding: channel c pairs with c + N/2 (first half, negated partner) or c - N/2 (second half)
-    const bool rope = !PLAIN && ROPE && s.rope_cos != nullptr;
+    const bool rope = ROPE && s.rope_cos != nullptr;
     const bool first_half = 2 * sg < per_row;
     const int64_t partner_off = first_half ? s.N / 2 : -(s.N / 2);
     const float partner_sign = first_half ? -1.0f : 1.0f;
@@ -414,7 +422,8 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
     // Site fields used in the loops, read once.
     const int64_t sx_t = s.sx_t, so_t = s.so_t, sd_t = s.sd_t, sm_t = s.sm_t, sg_t = s.sg_t, N = s.N;
     const bool has_packed = s.packed != nullptr, has_dense = !PLAIN && s.dense != nullptr;
-    const bool has_gated = !PLAIN && s.gated != nullptr;
+    // the plain streaming form has no slots for the multiplicand, and the plain rotary form is the q/k/v launch
+    const bool has_gated = !(PLAIN && (ASYNC || ROPE)) && s.gated != nullptr;
     const unsigned group_mask = 0xFu << (lane & 28);  // the four lanes that build one word together
     // byte selectors of the two exchange rounds of the 4 x 4 byte transpose (streaming plain form)
     const uint32_t sel_a = (lane & 1) ? 0x3715u : 0x6240u;  // even lane keeps timesteps 0 and 2 of its pair, odd 1 and 3
@@ -491,13 +500,15 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
         uint32_t* wp = has_packed && row_ok
             ? reinterpret_cast<uint32_t*>(s.packed) + out_row * s.so_tok + head * s.so_h + (sg >> 2) + sub * so_t
             : nullptr;
-        float rc[kSeg], rs[kSeg];
+        // The rotary factors are loaded here but unpacked only where they are used: touching them now would make the
+        // warp wait for this load before it has issued the loads of the currents.
+        Raw8<TX> cr, sr;
         if (rope) {
-            Raw8<TX> cr, sr;
             cr.load(static_cast<const TX*>(s.rope_cos) + tok * s.s_rope_tok + c0);
             sr.load(static_cast<const TX*>(s.rope_sin) + tok * s.s_rope_tok + c0);
-#pragma unroll
-            for (int c = 0; c < kSeg; ++c) { rc[c] = cr.get(c); rs[c] = sr.get(c); }
+        } else {
+            cr.clear();
+            sr.clear();
         }
 
         if (ASYNC && PLAIN && FULL) {
@@ -554,11 +565,29 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
             // The same channel-major form for launches too small to stream: the four timesteps straight from global
             // memory (four independent 16-byte loads per lane), T a multiple of four.
             for (int t0 = 0; t0 < T; t0 += kStepGroup) {
-                Raw8<TX> raw[kStepGroup];
+                Raw8<TX> raw[kStepGroup], mulv[kStepGroup];
 #pragma unroll
                 for (int i = 0; i < kStepGroup; ++i) raw[i].load(xp + i * sx_t);
+                if (has_gated) {
+#pragma unroll
+                    for (int i = 0; i < kStepGroup; ++i) mulv[i].load(mp + i * sm_t);
+                }
                 uint32_t bits[kStepGroup] = {0, 0, 0, 0};
-                if (t0 == 0) {
+                if (ROPE && rope) {
+                    // rotary embedding on the fly (T = 4 only, checked on the host): every operation rounded to the
+                    // model dtype, as the eager expression (x * cos) + (rotate_half(x) * sin) does
+                    Raw8<TX> partner[kStepGroup];
+#pragma unroll
+                    for (int i = 0; i < kStepGroup; ++i) partner[i].load(xp + i * sx_t + partner_off);
+                    float uf[kSeg];
+                    chain8_of<MODE>([&](int t, int c) {
+                        const float a = round_to<TX>(__fmul_rn(raw[t].get(c), cr.get(c)));
+                        const float r = round_to<TX>(__fmul_rn(partner_sign * partner[t].get(c), sr.get(c)));
+                        return round_to<TX>(__fadd_rn(a, r));
+                    }, b, th, uf, bits, std::make_integer_sequence<int, kSeg>{});
+#pragma unroll
+                    for (int c = 0; c < kSeg; ++c) st[c].init(uf[c], th[c]);
+                } else if (t0 == 0) {
                     float uf[kSeg];
                     chain8<MODE, TX>(raw, b, th, uf, bits, std::make_integer_sequence<int, kSeg>{});
                     // membrane after the fourth step; its pending reset (u > th) is what init derives
@@ -569,17 +598,31 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
                     for (int i = 0; i < kStepGroup; ++i)
                         step8<MODE, TX>(st, raw[i], b, th, bits[i], std::make_integer_sequence<int, kSeg>{});
                 }
-                uint32_t mine = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
-                if (all_live) {
-                    mine = __byte_perm(mine, __shfl_xor_sync(0xffffffffu, mine, 1), sel_a);
-                    mine = __byte_perm(mine, __shfl_xor_sync(0xffffffffu, mine, 2), sel_b);
-                } else {
-                    mine = __byte_perm(mine, __shfl_xor_sync(group_mask, mine, 1), sel_a);
-                    mine = __byte_perm(mine, __shfl_xor_sync(group_mask, mine, 2), sel_b);
+                if (has_gated) {
+                    // gated[t, tok, h, c] = spike ? mul[t, tok, h, c] : 0   (the spike * up product)
+#pragma unroll
+                    for (int i = 0; i < kStepGroup; ++i) {
+                        float g[kSeg];
+#pragma unroll
+                        for (int c = 0; c < kSeg; ++c) g[c] = (bits[i] >> c) & 1u ? mulv[i].get(c) : 0.0f;
+                        store8<TX>(gp + i * sg_t, g);
+                    }
+                    mp += kStepGroup * sm_t;
+                    gp += kStepGroup * sg_t;
                 }
-                if (wp != nullptr) {
-                    *wp = mine;
-                    wp += kStepGroup * so_t;
+                if (has_packed) {  // the same for the whole site, so the exchange below stays warp-uniform
+                    uint32_t mine = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+                    if (all_live) {
+                        mine = __byte_perm(mine, __shfl_xor_sync(0xffffffffu, mine, 1), sel_a);
+                        mine = __byte_perm(mine, __shfl_xor_sync(0xffffffffu, mine, 2), sel_b);
+                    } else {
+                        mine = __byte_perm(mine, __shfl_xor_sync(group_mask, mine, 1), sel_a);
+                        mine = __byte_perm(mine, __shfl_xor_sync(group_mask, mine, 2), sel_b);
+                    }
+                    if (wp != nullptr) {
+                        *wp = mine;
+                        wp += kStepGroup * so_t;
+                    }
                 }
                 xp += kStepGroup * sx_t;
             }
@@ -618,8 +661,8 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
                         float cur = x_i.get(c);
                         if (rope) {
                             // (x * cos) + (rotate_half(x) * sin), every operation rounded to the model dtype
-                            const float a = round_to<TX>(__fmul_rn(cur, rc[c]));
-                            const float r = round_to<TX>(__fmul_rn(partner_sign * partner_i.get(c), rs[c]));
+                            const float a = round_to<TX>(__fmul_rn(cur, cr.get(c)));
+                            const float r = round_to<TX>(__fmul_rn(partner_sign * partner_i.get(c), sr.get(c)));
                             cur = round_to<TX>(__fadd_rn(a, r));
                         }
                         st[c].template step<MODE>(cur, b[c], th[c], 1u << c, bits);
@@ -651,7 +694,7 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
 }
 
 template <int MODE, bool ROPE, bool FULL, bool ASYNC, bool PLAIN>
-__global__ void __launch_bounds__(kFusedThreads, ROPE ? 1 : (ASYNC ? 4 : 2))
+__global__ void __launch_bounds__(kFusedThreads, (ROPE && !PLAIN) ? 1 : (ASYNC ? 4 : 2))
 lif_pack_scatter_vec_kernel(VecArgs args, int T, int64_t n_tok, uint32_t* status) {
     // A next launch that asked to overlap this one (the attention after the q/k/v sites: it reads only lengths and
     // block tables until this grid has finished) may be placed from now on; without such a launch this does nothing.
@@ -946,10 +989,10 @@ extern "C" int spk_lif_pack_scatter(const spk_lif_site* sites, int n_sites, int 
             cudaStream_t vst = spk_stream(stream);
             const bool sub = reset_mode == SPK_RESET_SUBTRACT_DELAYED;
             const bool full = T % kStepGroup == 0;  // no partial group of timesteps: the per-step bounds checks drop out
-            bool plain = true;  // packed bits (+ final membrane) only: the feature tests fold away
-            for (int i = 0; i < n_sites; ++i)
-                plain = plain && sites[i].mem0 == nullptr && sites[i].dense == nullptr && sites[i].gated == nullptr &&
-                        sites[i].rope_cos == nullptr;
+            bool plain = true;  // packed bits, gated product, final membrane only: the other feature tests fold away
+            for (int i = 0; i < n_sites; ++i) plain = plain && sites[i].mem0 == nullptr && sites[i].dense == nullptr;
+            const bool plain_rope = plain && any_rope && !any_gated && T == kStepGroup;  // the decode step's q/k/v launch
+            plain = plain && !any_rope;
 #define SPK_LAUNCH_VEC(MODE_, ROPE_, FULL_, ASYNC_, PLAIN_)                                                                \
     do {                                                                                                              \
         auto kern = lif_pack_scatter_vec_kernel<MODE_, ROPE_, FULL_, ASYNC_, PLAIN_>;                                       \
@@ -962,8 +1005,9 @@ extern "C" int spk_lif_pack_scatter(const spk_lif_site* sites, int n_sites, int 
     } while (0)
 #define SPK_LAUNCH_MODE(MODE_)                                                          \
     do {                                                                                \
-        if (streaming && full && plain) SPK_LAUNCH_VEC(MODE_, false, true, true, true); \
+        if (streaming && full && plain && !any_gated) SPK_LAUNCH_VEC(MODE_, false, true, true, true); \
         else if (streaming) { if (full) SPK_LAUNCH_VEC(MODE_, false, true, true, false); else SPK_LAUNCH_VEC(MODE_, false, false, true, false); } \
+        else if (plain_rope) SPK_LAUNCH_VEC(MODE_, true, true, false, true); \
         else if (any_rope) { if (full) SPK_LAUNCH_VEC(MODE_, true, true, false, false); else SPK_LAUNCH_VEC(MODE_, true, false, false, false); } \
         else if (full && plain) SPK_LAUNCH_VEC(MODE_, false, true, false, true); \
         else { if (full) SPK_LAUNCH_VEC(MODE_, false, true, false, false); else SPK_LAUNCH_VEC(MODE_, false, false, false, false); } \
