@@ -293,7 +293,7 @@ def closed_loop(model, cfg, device, concurrency: int, n_requests: int, k: int = 
             "itl_ms_mean": round(statistics.mean(itl) * 1e3, 4), "wall_s": round(wall, 3),
             "decode_steps_per_host_visit": k, "host_visits": visits,
             "prefill": "batched popcount kernel over the packed pool" if packed_prefill
-                       else "per-sequence SDPA on unpacked spikes (the reference's arithmetic)"}
+                       else "SDPA on unpacked spikes, sequences of one shape in one call (the reference's arithmetic)"}
 
 
 def open_loop(model, cfg, device, rate: float = 8.0, n_requests: int = 64, seed: int = 78) -> dict:

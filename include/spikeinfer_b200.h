@@ -314,6 +314,13 @@ int spk_gather_kv_unpacked(const int32_t* cache, int64_t s_t, int64_t s_h, int64
                            int64_t s_slot, const int32_t* block_table, int64_t seq_len, int T,
                            int num_kv_heads, int head_dim, int block_size, int64_t num_blocks,
                            void* out, int out_dtype, uint32_t* status, void* stream);
+/* The same for n_seqs sequences of equal length in one launch: block_tables int32 [n_seqs, >= ceil(seq_len / bs)]
+ * with row stride sbt_n, out contiguous [n_seqs, T, H_kv, seq_len, head_dim].  Lets the prefill path read back all
+ * chunks of one shape at once instead of one launch per sequence (the reference loops, spikeinfer/attention.py:161-178). */
+int spk_gather_kv_unpacked_batch(const int32_t* cache, int64_t s_t, int64_t s_h, int64_t s_blk,
+                                 int64_t s_slot, const int32_t* block_tables, int64_t sbt_n, int64_t n_seqs,
+                                 int64_t seq_len, int T, int num_kv_heads, int head_dim, int block_size,
+                                 int64_t num_blocks, void* out, int out_dtype, uint32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------
  * On-GPU continuous-batching metadata for decode.  Replaces the decode half of

@@ -128,6 +128,9 @@ SIGNATURES = {
     "spk_gather_kv_unpacked": (c_int, [
         c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int,
         c_int64, c_void_p, c_int, c_void_p, c_void_p]),
+    "spk_gather_kv_unpacked_batch": (c_int, [
+        c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int,
+        c_int64, c_void_p, c_int, c_void_p, c_void_p]),
     "spk_meta_init": (c_int, [c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "spk_meta_advance": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

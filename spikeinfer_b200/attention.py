@@ -14,7 +14,8 @@ from dataclasses import dataclass, field
 import torch
 import torch.nn.functional as F
 
-from .kernels import LifSiteSpec, gather_kv_unpacked, lif_pack_scatter, pack_spikes, paged_spike_attn_decode
+from .kernels import (LifSiteSpec, gather_kv_unpacked, gather_kv_unpacked_batch, lif_pack_scatter, pack_spikes,
+                      paged_spike_attn_decode)
 from .kernels.packing import packed_width
 
 
@@ -109,18 +110,41 @@ def _flat_pool(pool: torch.Tensor) -> torch.Tensor:
 
 def _prefill_chunks(q_dense, k_cache, v_cache, meta, out, num_q_heads, num_kv_heads, head_dim):
     """q_dense ``[T, H_q, n_tok, D]`` (any strides): SDPA of every prefill chunk against its sequence's
-    cached prefix, read back from the packed pool (attention.py:161-178 of the reference)."""
+    cached prefix, read back from the packed pool (attention.py:161-178 of the reference).  The reference
+    loops over the sequences; here chunks of one shape (query length, total length) that lie next to each
+    other in the batch go through one read-back launch per pool and one SDPA call with the sequences as
+    leading batch entries: the same arithmetic per sequence, a fraction of the launches."""
     dtype, device = q_dense.dtype, q_dense.device
-    for i in range(meta.num_prefills):
+    T = q_dense.shape[0]
+    i, n = 0, meta.num_prefills
+    while i < n:
         start, q_len = meta.prefill_query_starts[i], meta.prefill_query_lens[i]
         total = meta.prefill_context_lens[i] + q_len
-        table = meta.prefill_block_tables[i]
-        k_all = gather_kv_unpacked(k_cache, table, total, head_dim, meta.block_size, dtype, status=meta.status)
-        v_all = gather_kv_unpacked(v_cache, table, total, head_dim, meta.block_size, dtype, status=meta.status)
-        o = F.scaled_dot_product_attention(
-            q_dense[:, :, start:start + q_len], k_all, v_all,
-            attn_mask=_causal_offset_mask(q_len, total, device, dtype), enable_gqa=num_q_heads != num_kv_heads)
-        out[:, start:start + q_len] = o.permute(0, 2, 1, 3)
+        j = i + 1
+        while (j < n and meta.prefill_query_lens[j] == q_len and meta.prefill_context_lens[j] + q_len == total
+               and meta.prefill_query_starts[j] == start + (j - i) * q_len):
+            j += 1
+        b = j - i
+        need = -(-total // meta.block_size)
+        mask = _causal_offset_mask(q_len, total, device, dtype)
+        if b == 1:
+            table = meta.prefill_block_tables[i]
+            k_all = gather_kv_unpacked(k_cache, table, total, head_dim, meta.block_size, dtype, status=meta.status)
+            v_all = gather_kv_unpacked(v_cache, table, total, head_dim, meta.block_size, dtype, status=meta.status)
+            o = F.scaled_dot_product_attention(q_dense[:, :, start:start + q_len], k_all, v_all, attn_mask=mask,
+                                               enable_gqa=num_q_heads != num_kv_heads)
+            out[:, start:start + q_len] = o.permute(0, 2, 1, 3)
+        else:
+            tables = torch.stack([t[:need].to(device=device, dtype=torch.int32) for t in meta.prefill_block_tables[i:j]])
+            k_all = gather_kv_unpacked_batch(k_cache, tables, total, head_dim, meta.block_size, dtype, status=meta.status)
+            v_all = gather_kv_unpacked_batch(v_cache, tables, total, head_dim, meta.block_size, dtype, status=meta.status)
+            # [T, H_q, b * q_len, D] -> [b * T, H_q, q_len, D], sequences leading
+            q = q_dense[:, :, start:start + b * q_len].unflatten(2, (b, q_len)).permute(2, 0, 1, 3, 4).flatten(0, 1)
+            o = F.scaled_dot_product_attention(q, k_all.flatten(0, 1), v_all.flatten(0, 1), attn_mask=mask,
+                                               enable_gqa=num_q_heads != num_kv_heads)
+            # [b * T, H_q, q_len, D] -> out[T, b * q_len, H_q, D]
+            out[:, start:start + b * q_len] = o.unflatten(0, (b, T)).permute(1, 0, 3, 2, 4).flatten(1, 2)
+        i = j
 
 
 def paged_attention(q_spk, k_spk, v_spk, k_cache, v_cache, meta: AttentionMetadata,

@@ -580,12 +580,15 @@ qk_scores_kernel(const uint32_t* __restrict__ q, int64_t sq_t, int64_t sq_n, int
 template <typename TO>
 __global__ void __launch_bounds__(256)
 gather_unpack_kernel(const uint32_t* __restrict__ cache, int64_t s_t, int64_t s_h, int64_t s_blk,
-                     int64_t s_slot, const int32_t* __restrict__ table, int64_t seq_len, int T,
+                     int64_t s_slot, const int32_t* __restrict__ table, int64_t sbt_n, int64_t seq_len, int T,
                      int Hkv, int D, int bs_log2, int64_t num_blocks, TO* __restrict__ out,
                      uint32_t* status) {
+    // grid.y = sequence: its row of the block tables, its [T, H_kv, seq_len, D] slab of the output
     const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     const int64_t total = static_cast<int64_t>(T) * Hkv * seq_len * D;
     if (idx >= total) return;
+    table += blockIdx.y * sbt_n;
+    out += blockIdx.y * total;
     int64_t rest = idx;
     const int c = static_cast<int>(rest % D); rest /= D;
     const int64_t s = rest % seq_len; rest /= seq_len;
@@ -731,24 +734,24 @@ extern "C" int spk_qk_scores(const int32_t* q, int64_t sq_t, int64_t sq_n, int64
     return SPK_OK;
 }
 
-extern "C" int spk_gather_kv_unpacked(const int32_t* cache, int64_t s_t, int64_t s_h, int64_t s_blk,
-                                      int64_t s_slot, const int32_t* block_table, int64_t seq_len,
-                                      int T, int num_kv_heads, int head_dim, int block_size,
-                                      int64_t num_blocks, void* out, int out_dtype, uint32_t* status,
-                                      void* stream) {
-    if (T < 0 || num_kv_heads < 1 || head_dim < 1 || seq_len < 0 || num_blocks < 1) return SPK_ERR_BAD_SHAPE;
+extern "C" int spk_gather_kv_unpacked_batch(const int32_t* cache, int64_t s_t, int64_t s_h, int64_t s_blk,
+                                            int64_t s_slot, const int32_t* block_tables, int64_t sbt_n,
+                                            int64_t n_seqs, int64_t seq_len, int T, int num_kv_heads, int head_dim,
+                                            int block_size, int64_t num_blocks, void* out, int out_dtype,
+                                            uint32_t* status, void* stream) {
+    if (T < 0 || num_kv_heads < 1 || head_dim < 1 || seq_len < 0 || num_blocks < 1 || n_seqs < 0) return SPK_ERR_BAD_SHAPE;
     const int bs_log2 = log2_exact(block_size);
     if (bs_log2 < 0) return SPK_ERR_UNSUPPORTED;
-    if (T == 0 || seq_len == 0) return SPK_OK;
-    if (cache == nullptr || block_table == nullptr || out == nullptr) return SPK_ERR_NULL_POINTER;
+    if (T == 0 || seq_len == 0 || n_seqs == 0) return SPK_OK;
+    if (cache == nullptr || block_tables == nullptr || out == nullptr) return SPK_ERR_NULL_POINTER;
     const int64_t total = static_cast<int64_t>(T) * num_kv_heads * seq_len * head_dim;
     const int64_t blocks = (total + 255) / 256;
-    if (blocks > 0x7fffffffLL) return SPK_ERR_TOO_LARGE;
-    const unsigned gsz = static_cast<unsigned>(blocks);
+    if (blocks > 0x7fffffffLL || n_seqs > 65535) return SPK_ERR_TOO_LARGE;
+    const dim3 gsz(static_cast<unsigned>(blocks), static_cast<unsigned>(n_seqs));
     cudaStream_t s = spk_stream(stream);
     const uint32_t* c = reinterpret_cast<const uint32_t*>(cache);
 #define SPK_GATHER(TO)                                                                          \
-    gather_unpack_kernel<TO><<<gsz, 256, 0, s>>>(c, s_t, s_h, s_blk, s_slot, block_table, seq_len, T, \
+    gather_unpack_kernel<TO><<<gsz, 256, 0, s>>>(c, s_t, s_h, s_blk, s_slot, block_tables, sbt_n, seq_len, T, \
                                                  num_kv_heads, head_dim, bs_log2, num_blocks,  \
                                                  static_cast<TO*>(out), status)
     switch (out_dtype) {
@@ -761,6 +764,15 @@ extern "C" int spk_gather_kv_unpacked(const int32_t* cache, int64_t s_t, int64_t
 #undef SPK_GATHER
     SPK_CHECK_LAUNCH();
     return SPK_OK;
+}
+
+extern "C" int spk_gather_kv_unpacked(const int32_t* cache, int64_t s_t, int64_t s_h, int64_t s_blk,
+                                      int64_t s_slot, const int32_t* block_table, int64_t seq_len,
+                                      int T, int num_kv_heads, int head_dim, int block_size,
+                                      int64_t num_blocks, void* out, int out_dtype, uint32_t* status,
+                                      void* stream) {
+    return spk_gather_kv_unpacked_batch(cache, s_t, s_h, s_blk, s_slot, block_table, 0, 1, seq_len, T, num_kv_heads,
+                                        head_dim, block_size, num_blocks, out, out_dtype, status, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -14,6 +14,7 @@ from .sampling import argmax_rows, argmax_workspace_bytes
 from .packing import BITS_PER_WORD, pack_spikes, packed_bytes_per_token, packed_width, unpack_spikes
 from .spike_attention import (
     gather_kv_unpacked,
+    gather_kv_unpacked_batch,
     paged_spike_attn_decode,
     paged_spike_attn_decode_noalloc,
     qk_scores,
@@ -39,5 +40,6 @@ __all__ = [
     "paged_spike_attn_decode",
     "paged_spike_attn_decode_noalloc",
     "gather_kv_unpacked",
+    "gather_kv_unpacked_batch",
     "qk_scores",
 ]

@@ -147,6 +147,33 @@ def gather_kv_unpacked(cache: torch.Tensor, block_table: torch.Tensor, seq_len: 
     return out
 
 
+def gather_kv_unpacked_batch(cache: torch.Tensor, block_tables: torch.Tensor, seq_len: int, head_dim: int,
+                             block_size: int, dtype: torch.dtype, status=None) -> torch.Tensor:
+    """:func:`gather_kv_unpacked` for several sequences of the same length in one launch: ``block_tables`` int32
+    ``[n_seqs, >= ceil(seq_len / block_size)]`` -> dense ``[n_seqs, T, H_kv, seq_len, head_dim]``."""
+    _lib.require_cuda(cache, "gather_kv_unpacked_batch cache")
+    T, H = cache.shape[0], cache.shape[1]
+    n = block_tables.shape[0]
+    out = torch.empty((n, T, H, seq_len, head_dim), dtype=dtype, device=cache.device)
+    if out.numel() == 0:
+        return out
+    if block_tables.dtype != torch.int32 or block_tables.ndim != 2:
+        raise TypeError("block_tables must be int32 [n_seqs, blocks]")
+    if block_tables.shape[1] * block_size < seq_len:
+        raise ValueError("block tables shorter than seq_len")
+    if block_tables.stride(1) != 1:
+        block_tables = block_tables.contiguous()
+    s = _pool_strides(cache, block_size)
+    lib = _lib.load()
+    with torch.cuda.device(cache.device):
+        rc = lib.spk_gather_kv_unpacked_batch(cache.data_ptr(), s[0], s[1], s[2], s[3], block_tables.data_ptr(),
+                                              block_tables.stride(0), n, seq_len, T, H, head_dim, block_size, s[4],
+                                              out.data_ptr(), _lib.dtype_code(dtype), _lib.ptr(status),
+                                              _lib.current_stream(cache.device))
+    _lib.check(rc, "spk_gather_kv_unpacked_batch")
+    return out
+
+
 def paged_spike_attn_decode_noalloc(q_packed, k_cache, v_cache, block_tables, seq_lens, head_dim: int,
                                     block_size: int, num_q_heads: int, num_kv_heads: int, out: torch.Tensor,
                                     status: torch.Tensor | None = None) -> torch.Tensor:

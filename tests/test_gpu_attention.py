@@ -177,6 +177,25 @@ def test_gather_kv_unpacked(dev, golden):
     assert torch.equal(got.cpu(), want)
 
 
+def test_gather_kv_unpacked_batch_equals_the_per_sequence_read(dev):
+    case = cases.attention_case(seq_lens=[40, 97, 64, 130, 40], seed=12)
+    d = to_dev(case, dev)
+    for cache in ("k_cache", "v_cache"):
+        for dtype in (torch.float32, torch.bfloat16):
+            got = kernels.gather_kv_unpacked_batch(d[cache], d["block_tables"][[0, 4, 2]], 40, 64, 16, dtype)
+            assert got.shape == (3, 4, 2, 40, 64)
+            for b, row in enumerate((0, 4, 2)):
+                want = orc.gather_kv_unpacked(case[cache], case["block_tables"][row], 40, 64, 16, dtype)
+                assert torch.equal(got[b].cpu(), want)
+    # a strided view of the tables (row stride above the width) and an empty batch
+    wide = d["block_tables"][:, :3]
+    got = kernels.gather_kv_unpacked_batch(d["k_cache"], wide, 40, 64, 16, torch.float32)
+    assert torch.equal(got[1].cpu(), orc.gather_kv_unpacked(case["k_cache"], case["block_tables"][1], 40, 64, 16, torch.float32))
+    assert kernels.gather_kv_unpacked_batch(d["k_cache"], wide[:0], 40, 64, 16, torch.float32).shape[0] == 0
+    with pytest.raises(ValueError):
+        kernels.gather_kv_unpacked_batch(d["k_cache"], wide, 64, 64, 16, torch.float32)  # 3 pages hold 48 keys
+
+
 def config2_case(seed=2, n=64, lo=128, hi=4096):
     g = cases.gen(seed)
     lens = torch.randint(lo, hi + 1, (n,), generator=g).tolist()
