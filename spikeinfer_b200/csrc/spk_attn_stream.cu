@@ -183,10 +183,13 @@ __device__ __forceinline__ void store_channels(TO* dst, const float* src, float 
 }
 
 #ifndef SPK_STREAM_MINB
-#define SPK_STREAM_MINB 5
+#define SPK_STREAM_MINB 4
 #endif
 
-constexpr int kShortSteps = 8;   // an item of at most this many 32-key steps (256 keys) is never cut between warps
+#ifndef SPK_SHORT_STEPS
+#define SPK_SHORT_STEPS 8
+#endif
+constexpr int kShortSteps = SPK_SHORT_STEPS;  // an item of at most this many 32-key steps (256 keys) is never cut between warps
 constexpr int kUncutSteps = 24;  // tables of at most this many steps (768 keys): nothing is cut at all.  One warp walks such
                                  // a row in under 5 us, about what the combine pass adds to a call once anything may be cut
 
