@@ -196,7 +196,10 @@ constexpr int kUncutSteps = 24;  // tables of at most this many steps (768 keys)
 template <int W>
 struct StreamSmem {
     static constexpr int D = 32 * W;
-    static constexpr int STAGES = W == 2 ? 4 : 3;        // 64-key tiles in flight per warp
+#ifndef SPK_STREAM_STAGES2
+#define SPK_STREAM_STAGES2 4
+#endif
+    static constexpr int STAGES = W == 2 ? SPK_STREAM_STAGES2 : 3;  // 64-key tiles in flight per warp
     static constexpr int HALF_WORDS = kTileKeys * W;     // words of a tile's K rows (and of its V rows)
     static constexpr int TILE_WORDS = 2 * HALF_WORDS;    // K rows then V rows
     static constexpr int ES = D + 4;                     // row stride of the epilogue's transposition buffer
