@@ -286,10 +286,13 @@ def test_streaming_form_edges(reset_mode, dev):
 
 
 # ------------------------------------------------------------------ fused RoPE, gated product, add + RMSNorm
+@pytest.mark.parametrize("reset_mode", [orc.SUBTRACT_DELAYED, orc.HARD_ZERO], ids=["subtract_delayed", "hard_zero"])
+@pytest.mark.parametrize("T,D", [(4, 64), (4, 128), (8, 64)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
-def test_fused_rope_is_bit_exact_with_the_eager_expression(dtype, dev):
-    """(x * cos) + (rotate_half(x) * sin), every op rounded to the model dtype (modeling_fast.py:89-99), then LIF."""
-    T, n_tok, H, D = 4, 29, 3, 64
+def test_fused_rope_is_bit_exact_with_the_eager_expression(dtype, T, D, reset_mode, dev):
+    """(x * cos) + (rotate_half(x) * sin), every op rounded to the model dtype (modeling_fast.py:89-99), then LIF.
+    T = 4 takes the channel-major form with the rotation on the fly, T = 8 the per-timestep form."""
+    n_tok, H = 29, 3
     g = cases.gen(91)
     x = (torch.randn(T, n_tok, H, D, generator=g) * 1.5).to(dtype)
     pos = torch.randint(0, 4000, (n_tok,), generator=g)
@@ -299,12 +302,13 @@ def test_fused_rope_is_bit_exact_with_the_eager_expression(dtype, dev):
     rot = torch.cat((-x[..., D // 2:], x[..., : D // 2]), dim=-1)
     want_cur = (x * cos[None, :, None, :]) + (rot * sin[None, :, None, :])
     beta, th = torch.rand(D, generator=g), torch.rand(D, generator=g) * 0.9 + 0.1
-    want_s, want_u = orc.lif_multistep(want_cur, beta, th, out_dtype=torch.uint8)
-    packed = torch.empty(T, n_tok, H, 2, dtype=torch.int32, device=dev)
+    want_s, want_u = orc.lif_multistep(want_cur, beta, th, out_dtype=torch.uint8, reset_mode=reset_mode)
+    W = D // 32
+    packed = torch.empty(T, n_tok, H, W, dtype=torch.int32, device=dev)
     mem = torch.empty(n_tok, H, D, device=dev)
     kernels.lif_pack_scatter([kernels.LifSiteSpec(
-        x=x.to(dev), beta=beta.to(dev), threshold=th.to(dev), packed=packed, packed_strides=(n_tok * H * 2, H * 2, 2),
-        mem_out=mem, rope_cos=cos.to(dev), rope_sin=sin.to(dev))])
+        x=x.to(dev), beta=beta.to(dev), threshold=th.to(dev), packed=packed, packed_strides=(n_tok * H * W, H * W, W),
+        mem_out=mem, rope_cos=cos.to(dev), rope_sin=sin.to(dev))], reset_mode=reset_mode)
     assert torch.equal(packed.cpu(), orc.pack_spikes(want_s))
     assert torch.equal(mem.cpu(), want_u)
 
