@@ -116,7 +116,12 @@ class ClockSampler:
 
     def __exit__(self, *exc):
         if self.proc is not None:
+            # nvidia-smi needs up to a second or two before its first line on a host with eight GPUs: give it the
+            # chance to deliver a sample (the GPU is still clocked up from the region that just ended)
+            deadline = time.time() + 3.0
             time.sleep(0.15)
+            while not self.samples and time.time() < deadline and self.proc.poll() is None:
+                time.sleep(0.05)
             self.proc.terminate()  # the exact child started above
             try:
                 self.proc.wait(timeout=5)
@@ -641,20 +646,20 @@ def run_own(args) -> None:
         return start.elapsed_time(stop)
 
     # ---- value: tokens stay on the device; the first region is the headline, the others its spread -------
-    for _ in range(W):
-        engine.decode_step()
-    torch.cuda.synchronize(device)
-    snap = engine.snapshot()
-    with ClockSampler(local) as clocks:
+    with ClockSampler(local) as clocks:  # started ahead of the warm-up so that it is sampling when the clock starts
+        for _ in range(W):
+            engine.decode_step()
+        torch.cuda.synchronize(device)
+        snap = engine.snapshot()
         if args.profiler_range:
             torch.cuda.profiler.start()
         ms = timed_steps(engine)
         if args.profiler_range:
             torch.cuda.profiler.stop()
-    regions = [ms]
-    for _ in range(R - 1):
-        engine.restore(snap)
-        regions.append(timed_steps(engine))
+        regions = [ms]
+        for _ in range(R - 1):
+            engine.restore(snap)
+            regions.append(timed_steps(engine))
     # ---- e2e: host-in-the-loop steps ---------------------------------------
     def timed_host_steps() -> float:
         barrier()
@@ -863,14 +868,14 @@ def run_tp7b(args) -> None:
         if world > 1:
             dist.barrier()
 
-    for _ in range(W):
-        engine.decode_step()
-    torch.cuda.synchronize(device)
-    stage("warm-up replays done")
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    stage("barrier passed")
-    with ClockSampler(local) as clocks:
+    with ClockSampler(local) as clocks:  # started ahead of the warm-up so that it is sampling when the clock starts
+        for _ in range(W):
+            engine.decode_step()
+        torch.cuda.synchronize(device)
+        stage("warm-up replays done")
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        stage("barrier passed")
         start.record()
         for _ in range(K):
             engine.decode_step()
