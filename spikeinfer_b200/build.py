@@ -21,9 +21,11 @@ LIB_PATH = PKG_DIR / "libspikeinfer_b200.so"
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
-    "--fmad=false",  # the LIF contract forbids contraction; nothing else here depends on FMA
     "-Xcompiler", "-fPIC",
 ]
+# Translation units whose arithmetic contract forbids contracting a multiply and an add into one rounding: the LIF
+# recurrence (every product and sum is rounded on its own, as the reference does) and the RMSNorm's mean + eps.
+NO_FMA_CONTRACTION = {"spk_lif.cu", "spk_norm.cu"}
 
 
 def _nvcc() -> str:
@@ -56,6 +58,8 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     for src in sources():
         obj = obj_dir / (src.stem + ".o")
         cmd = [nvcc, *NVCC_FLAGS, "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
+        if src.name in NO_FMA_CONTRACTION:
+            cmd.insert(1, "--fmad=false")
         if ptxas_info:
             cmd[1:1] = ["-Xptxas", "-v"]
         if verbose:
