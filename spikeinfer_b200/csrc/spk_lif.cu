@@ -693,6 +693,120 @@ __device__ __forceinline__ void fused_site_vec(const spk_lif_site& s, uint32_t u
     }
 }
 
+// The streaming plain form on its own (T = 4, no rotary embedding, no initial membrane, dense spikes or gated
+// product): the same copies, arithmetic and stores as fused_site_vec<.., ASYNC, PLAIN> would issue, with the
+// per-token bookkeeping reduced to running pointers and 32-bit counters.  At 11 instructions per element-step that
+// bookkeeping was 40 % of the issue slots of an issue-bound kernel.
+template <typename TX, int MODE>
+__device__ __forceinline__ void stream_plain_site(const spk_lif_site& s, uint32_t units, uint32_t per_tok,
+                                                  uint32_t per_row, int toks, uint32_t unit, int lane, int64_t n_tok,
+                                                  uint32_t* status, uint4* stage, int slots) {
+    if (unit >= units) return;  // the lanes of a word (4 consecutive units) are in or out together: units % 4 == 0
+    const uint32_t grp = unit / per_tok;
+    const uint32_t idx = unit - grp * per_tok;
+    const uint32_t h = s.H == 1 ? 0u : idx / per_row;
+    const uint32_t sg = idx - h * per_row;
+    const int c0 = static_cast<int>(sg) * kSeg;
+    const int sub = lane & 3;
+    const unsigned group_mask = 0xFu << (lane & 28);
+    const uint32_t sel_a = (lane & 1) ? 0x3715u : 0x6240u;
+    const uint32_t sel_b = (lane & 2) ? 0x3276u : 0x5410u;
+    constexpr int VECS = sizeof(TX) * kSeg / 16;
+
+    const int64_t tok0 = static_cast<int64_t>(grp) * toks;
+    const int64_t left64 = n_tok - tok0;
+    const int n_mine = left64 < toks ? static_cast<int>(left64 > 0 ? left64 : 0) : toks;  // tokens of this lane's walk
+    const int64_t sx_tok = s.sx_tok, sx_t = s.sx_t, so_tok = s.so_tok;
+    const TX* xi = static_cast<const TX*>(s.x) + tok0 * sx_tok + static_cast<int64_t>(h) * s.sx_h + c0;  // next token to copy
+    const uint32_t stage_bytes = static_cast<uint32_t>(slots) * 32u * 16u;
+    const uint32_t stage0 = static_cast<uint32_t>(__cvta_generic_to_shared(stage));
+    uint32_t fill = 0;  // byte offset of the stage the next copy goes to
+    int issued = 0;
+    auto issue = [&]() {
+        if (issued < n_mine) {
+            const TX* p0 = xi;
+#pragma unroll
+            for (int i = 0; i < kStepGroup; ++i) {
+#pragma unroll
+                for (int v = 0; v < VECS; ++v) {
+                    const uint32_t dst = stage0 + fill + static_cast<uint32_t>((i * VECS + v) * 32 * 16);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(p0 + v * (16 / sizeof(TX))));
+                }
+                p0 += sx_t;
+            }
+            xi += sx_tok;
+        }
+        ++issued;
+        fill = fill == (kStages - 1) * stage_bytes ? 0u : fill + stage_bytes;
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int jj = 0; jj < kStages - 1; ++jj) issue();
+
+    // weights of this lane's 8 channels (after the first copies are on their way)
+    float b[kSeg], th[kSeg];
+    {
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(s.beta + c0));
+        const float4 b1 = __ldg(reinterpret_cast<const float4*>(s.beta + c0) + 1);
+        const float4 t0 = __ldg(reinterpret_cast<const float4*>(s.threshold + c0));
+        const float4 t1 = __ldg(reinterpret_cast<const float4*>(s.threshold + c0) + 1);
+        const float bb[kSeg] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        const float tt[kSeg] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+#pragma unroll
+        for (int i = 0; i < kSeg; ++i) {
+            b[i] = clamp_beta(bb[i]);
+            th[i] = tt[i];
+        }
+    }
+    const bool scatter = s.packed != nullptr && s.slot_mapping != nullptr;
+    const int64_t* slot_p = scatter ? s.slot_mapping + tok0 : nullptr;
+    uint32_t* wbase = s.packed != nullptr
+        ? reinterpret_cast<uint32_t*>(s.packed) + static_cast<int64_t>(h) * s.so_h + (sg >> 2) + sub * s.so_t
+        : nullptr;
+    uint32_t* wp = wbase != nullptr && !scatter ? wbase + tok0 * so_tok : nullptr;  // running, when rows are the tokens
+    const int64_t mem_step = static_cast<int64_t>(s.H) * s.N;
+    float* mo = s.mem_out != nullptr ? s.mem_out + (tok0 * s.H + h) * s.N + c0 : nullptr;
+    uint32_t drain = 0;  // byte offset of the stage the next token is read from
+
+    for (int j = 0; j < toks; ++j) {
+        issue();
+        cp_async_wait<kStages - 1>();  // this lane's copies for token j have landed
+        const bool live = j < n_mine;
+        const bool all_live = __all_sync(0xffffffffu, live);
+        const uint4* mine_stage = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(stage) + drain);
+        drain = drain == (kStages - 1) * stage_bytes ? 0u : drain + stage_bytes;
+        if (!live) continue;
+        Raw8<TX> raw[kStepGroup];
+#pragma unroll
+        for (int i = 0; i < kStepGroup; ++i) raw[i].from_smem(mine_stage + i * VECS * 32);
+        float uf[kSeg];
+        uint32_t bits[kStepGroup] = {0, 0, 0, 0};
+        chain8<MODE, TX>(raw, b, th, uf, bits, std::make_integer_sequence<int, kSeg>{});
+        uint32_t mine = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+        if (all_live) {
+            mine = __byte_perm(mine, __shfl_xor_sync(0xffffffffu, mine, 1), sel_a);
+            mine = __byte_perm(mine, __shfl_xor_sync(0xffffffffu, mine, 2), sel_b);
+        } else {
+            mine = __byte_perm(mine, __shfl_xor_sync(group_mask, mine, 1), sel_a);
+            mine = __byte_perm(mine, __shfl_xor_sync(group_mask, mine, 2), sel_b);
+        }
+        if (scatter) {
+            const int64_t out_row = slot_p[j];
+            if (out_row >= 0 && out_row < s.num_rows) wbase[out_row * so_tok] = mine;
+            else if (sg == 0) spk_flag(status, SPK_STATUS_BAD_SLOT);
+        } else if (wp != nullptr) {
+            *wp = mine;
+            wp += so_tok;
+        }
+        if (mo != nullptr) {
+            float4* o = reinterpret_cast<float4*>(mo);
+            o[0] = make_float4(uf[0], uf[1], uf[2], uf[3]);
+            o[1] = make_float4(uf[4], uf[5], uf[6], uf[7]);
+            mo += mem_step;
+        }
+    }
+}
+
 template <int MODE, bool ROPE, bool FULL, bool ASYNC, bool PLAIN>
 __global__ void __launch_bounds__(kFusedThreads, (ROPE && !PLAIN) ? 1 : (ASYNC ? 4 : 2))
 lif_pack_scatter_vec_kernel(VecArgs args, int T, int64_t n_tok, uint32_t* status) {
@@ -707,9 +821,16 @@ lif_pack_scatter_vec_kernel(VecArgs args, int T, int64_t n_tok, uint32_t* status
     const spk_lif_site& s = args.s[site];
     // this lane's slots: [warp][stage][slot][lane]
     uint4* stage = ASYNC ? stage_smem + (threadIdx.x >> 5) * kStages * args.slots * 32 + lane : nullptr;
-#define SPK_SITE(TX_) \
-    fused_site_vec<TX_, MODE, ROPE, FULL, ASYNC, PLAIN>(s, args.units[site], args.per_tok[site], args.per_row[site], \
-                                                 args.toks, unit, lane, T, n_tok, status, stage, args.slots)
+#define SPK_SITE(TX_)                                                                                              \
+    do {                                                                                                            \
+        if (ASYNC && PLAIN && FULL && !ROPE)                                                                        \
+            stream_plain_site<TX_, MODE>(s, args.units[site], args.per_tok[site], args.per_row[site], args.toks,    \
+                                         unit, lane, n_tok, status, stage, args.slots);                             \
+        else                                                                                                        \
+            fused_site_vec<TX_, MODE, ROPE, FULL, ASYNC, PLAIN>(s, args.units[site], args.per_tok[site],            \
+                                                                args.per_row[site], args.toks, unit, lane, T, n_tok, \
+                                                                status, stage, args.slots);                         \
+    } while (0)
     switch (s.x_dtype) {
         case SPK_F32: SPK_SITE(float); break;
         case SPK_BF16: SPK_SITE(__nv_bfloat16); break;
