@@ -186,6 +186,10 @@ __device__ __forceinline__ void store_channels(TO* dst, const float* src, float 
 #define SPK_STREAM_MINB 4
 #endif
 
+#ifndef SPK_STREAM_MINB4
+#define SPK_STREAM_MINB4 3
+#endif
+
 #ifndef SPK_SHORT_STEPS
 #define SPK_SHORT_STEPS 8
 #endif
@@ -445,7 +449,7 @@ __device__ __forceinline__ int64_t range_of(const RangeSplit& r, int64_t x) {
 // after it (slot 1).
 // Otherwise: one warp per (unit of unit_keys keys, gt), units enumerated as row * max_units + unit.
 template <int W, int NB, bool DENSE>
-__global__ void __launch_bounds__(kThreads, (W == 2 ? (NB == 1 ? SPK_STREAM_MINB : 4) : (NB == 1 ? 4 : 3)))
+__global__ void __launch_bounds__(kThreads, (W == 2 ? (NB == 1 ? SPK_STREAM_MINB : 4) : (NB == 1 ? SPK_STREAM_MINB4 : 3)))
 attn_stream_kernel(const AttnParams p, const StreamParams sp) {
     using S = StreamSmem<W>;
     constexpr int D = S::D;
@@ -1072,7 +1076,7 @@ int spk_attn_selected_form() { return g_attn_form.load(std::memory_order_relaxed
 // CTAs per SM the main kernel is built for (its __launch_bounds__), by rows of words and weight blocks.
 static int stream_ctas_per_sm(int head_dim, bool wide) {
     if (head_dim == 64) return wide ? 4 : SPK_STREAM_MINB;
-    return wide ? 3 : 4;
+    return wide ? 3 : SPK_STREAM_MINB4;
 }
 
 StreamPlan spk_attn_stream_plan(int T, int64_t n_seqs, int Hq, int Hkv, int head_dim, int block_size,
