@@ -39,7 +39,7 @@ constexpr int kTblMax = 128;       // block-table entries staged per unit (2048 
 constexpr int kDenseRows = 1024;   // up to this many sequences the units are enumerated densely
 constexpr int kScaleLog2 = 14;     // weights are kept times 2^14: the largest is 2^14, the smallest used 2^14 e^-24
 constexpr float kLoUnscale = 1.0f / 2048.0f;  // the lo half of a weight is stored times 2^11
-constexpr int kResidentWarpsTarget = 148 * 20;
+constexpr int kResidentWarpsTarget = 148 * 20;  // unit form: units are made smaller until the call has twice this many
 
 constexpr int kXGroup = 32 * 4 + 16;  // words between two groups of four byte-words in the regrouped V tile (padded: bank spread)
 
