@@ -177,6 +177,44 @@ def test_gather_kv_unpacked(dev, golden):
     assert torch.equal(got.cpu(), want)
 
 
+@pytest.mark.parametrize("seed", range(16))
+def test_random_batches_through_every_work_split(seed, dev):
+    """Seeded random batches that land in every way the streaming form splits work: nothing cut and a warp per item
+    (tables of up to 768 keys), nothing cut but more items than resident warps, equal step ranges with cut rows and
+    the combine pass, and more than 1024 rows (one warp per unit); ragged lengths down to 1, head_dim 64 and 128,
+    several GQA ratios and timestep counts, fp32 against the oracle at 1e-5 and bf16 within the 16-bit bar, and the
+    same through the overlapped launch."""
+    g = cases.gen(1000 + seed)
+    pick = lambda xs: xs[int(torch.randint(0, len(xs), (1,), generator=g))]
+    head_dim = pick([64, 64, 128])
+    hq, hkv = pick([(14, 2), (7, 1), (4, 2), (8, 8), (16, 2), (28, 4)])
+    T = pick([1, 4, 4, 8])
+    kind = seed % 4
+    if kind == 0:      # short tables: nothing is cut, one warp per item
+        n, hi, max_blocks = pick([1, 5, 64]), pick([40, 200, 700]), 48
+    elif kind == 1:    # short tables, many rows: more items than resident warps
+        n, hi, max_blocks = 700, 90, 8
+    elif kind == 2:    # long tables: equal step ranges, cut rows, combine pass
+        n, hi, max_blocks = pick([2, 9, 24]), pick([900, 2500]), 256
+    else:              # beyond 1024 rows: the unit form
+        n, hi, max_blocks = 1100, 70, 64
+    lens = torch.randint(1, hi + 1, (n,), generator=g).tolist()
+    if n > 3:
+        lens[0], lens[-1] = hi, 1
+    case = cases.attention_case(seq_lens=lens, head_dim=head_dim, num_q_heads=hq, num_kv_heads=hkv, T=T,
+                                density=pick([0.1, 0.3]), seed=2000 + seed, max_blocks=max_blocks)
+    d = to_dev(case, dev)
+    want = orc.paged_spike_attn_decode(**case)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    got = kernels.paged_spike_attn_decode(**d, status=status)
+    assert rel_err(got.cpu(), want) < REL_TOL, f"fp32: {rel_err(got.cpu(), want):.2e}"
+    got16 = kernels.paged_spike_attn_decode(**d, dtype=torch.bfloat16, status=status)
+    assert within_bf16_bar(got16.cpu(), want)
+    again = kernels.paged_spike_attn_decode(**d, status=status, overlap_previous=True)
+    assert torch.equal(again, got)
+    assert status.item() == 0
+
+
 def test_gather_kv_unpacked_batch_equals_the_per_sequence_read(dev):
     case = cases.attention_case(seq_lens=[40, 97, 64, 130, 40], seed=12)
     d = to_dev(case, dev)
