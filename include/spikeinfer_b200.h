@@ -275,7 +275,7 @@ int spk_attn_select_form(int form);
  *    is refused with SPK_ERR_STATIC_SCRATCH_TOO_SMALL and nothing is launched.  Tables of up to
  *    256 keys per sequence (max_blocks * block_size) need no scratch at all.  Beyond that the need
  *    grows with n_seqs * T * H_kv * max_blocks * block_size (two records of 8 * head_dim + 8 floats
- *    per warp that shares the work, up to 2368 warps, plus the rows' step prefix): at T=4, 14/2
+ *    per warp that shares the work, up to 2368 warps): at T=4, 14/2
  *    heads, head_dim 64, 15 sequences of up to 4096 keys need 7.99 MB and fit, 16 such sequences
  *    (8.52 MB) do not.
  *  - The first call on each device, whatever its sizes (a problem that needs no scratch included),

@@ -36,7 +36,7 @@ struct StreamPlan {
     int max_units;      // unit form: units of the longest possible row
     int passes;         // passes per KV head (eight query heads each)
     int64_t rec_floats; // floats per partial record: 8 * head_dim sums + 8 weight totals
-    int64_t ws_bytes;   // partial records (and, range form, the step prefix); 0 when nothing can be cut
+    int64_t ws_bytes;   // partial records; 0 when nothing can be cut
 };
 
 // Form picked by spk_attn_select_form (SPK_ATTN_FORM_*).

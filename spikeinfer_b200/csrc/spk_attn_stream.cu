@@ -53,7 +53,6 @@ struct StreamParams {
     int64_t rec;      // floats per partial record
     int64_t workers;  // warps that share the step list (range form)
     float* dense_ws;  // two record slots per worker (range form)
-    int* prefix_out;  // where the first CTA leaves the step prefix for the combine pass (range form)
 };
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -523,12 +522,6 @@ attn_stream_kernel(const AttnParams p, const StreamParams sp) {
     const int64_t worker = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
 
     if (DENSE) {
-        // the first CTA leaves the step prefix where the combine pass finds it
-        if (blockIdx.x == 0 && sp.prefix_out != nullptr) {
-            // when this launch overlaps the one before it, the previous call's combine pass may still read its copy
-            if (p.overlap) asm volatile("griddepcontrol.wait;" ::: "memory");
-            for (int i = threadIdx.x; i <= n_seqs; i += kThreads) sp.prefix_out[i] = prefix[i];
-        }
         if (worker >= sp.workers) return;
         const int64_t total = static_cast<int64_t>(prefix[n_seqs]) * sp.gt;
         // this warp's range of the step list; a short item belongs, whole, to the range it starts in
@@ -960,7 +953,7 @@ attn_tc_kernel(const AttnParams p, const StreamParams sp) {
 
 // Sums the partial records of one (sequence, KV head, pass, timestep) in key order and divides.  Items that one
 // warp finished alone were written by the main kernel and are skipped.  A thread owns four channels of one head;
-// the records' values are fetched four records at a time (independent loads) and added in record order.
+// the records' values are fetched eight records at a time (independent loads) and added in record order.
 __global__ void __launch_bounds__(128)
 attn_stream_combine_kernel(const AttnParams p, const StreamParams sp, int D) {
     // a following launch that asked to overlap (it waits for this grid before it touches q, K/V or the records)
@@ -980,24 +973,42 @@ attn_stream_combine_kernel(const AttnParams p, const StreamParams sp, int D) {
     const int pass = gp - g * p.passes;
     const int h0 = g * p.n_rep + pass * kAttnHeads;
     const int nh = min(kAttnHeads, p.n_rep - pass * kAttnHeads);
-    // the records (and the step prefix) are complete once the main kernel's grid has finished and flushed
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    // records of this item: count, and where record i lies
+    // records of this item: count, and where record i lies.  All of it follows from the lengths, so it is worked
+    // out here, while the main kernel still runs.
     int n_rec;
     int64_t first = 0;
     if (sp.dense) {
+        // steps of the rows before this one, and of all rows (the main kernel's step prefix, recomputed)
+        __shared__ int red[2][4];
+        int before = 0, all = 0;
+        for (int r = threadIdx.x; r < static_cast<int>(p.n_seqs); r += blockDim.x) {
+            const int st = steps_of(clamp_len(__ldg(p.lens + r), p.max_keys));
+            all += st;
+            if (r < row) before += st;
+        }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+            before += __shfl_xor_sync(0xffffffffu, before, o);
+            all += __shfl_xor_sync(0xffffffffu, all, o);
+        }
+        if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = before; red[1][threadIdx.x >> 5] = all; }
+        __syncthreads();
+        before = red[0][0] + red[0][1] + red[0][2] + red[0][3];
+        all = red[1][0] + red[1][1] + red[1][2] + red[1][3];
         // the item's interval of the step list; piece i belongs to worker first + i: the first one started the
         // item (slot 1), the others continued it (slot 0)
-        const int64_t total = static_cast<int64_t>(sp.prefix_out[p.n_seqs]) * sp.gt;
+        const int64_t total = static_cast<int64_t>(all) * sp.gt;
         const RangeSplit split = make_split(total, sp.workers);
         const int nsteps = steps_of(len);
-        const int64_t g0 = static_cast<int64_t>(sp.prefix_out[row]) * sp.gt + static_cast<int64_t>(gt) * nsteps;
+        const int64_t g0 = static_cast<int64_t>(before) * sp.gt + static_cast<int64_t>(gt) * nsteps;
         first = range_of(split, g0);
         n_rec = static_cast<int>(range_of(split, g0 + nsteps - 1) - first) + 1;
         if (n_rec <= 1) return;
     } else {
         n_rec = units_of(len, sp.unit_log2);
     }
+    // the records are complete once the main kernel's grid has finished and flushed
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     auto record = [&](int u) -> const float* {
         return sp.dense ? sp.dense_ws + (2 * (first + u) + (u == 0 ? 1 : 0)) * sp.rec : p.ws + (item * sp.max_units + u) * sp.rec;
     };
@@ -1007,17 +1018,18 @@ attn_stream_combine_kernel(const AttnParams p, const StreamParams sp, int D) {
         const int d = 4 * (idx - hh * quads);
         float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         float l = 0.0f;
-        for (int u0 = 0; u0 < n_rec; u0 += 4) {
-            float4 v[4];
-            float w[4];
+        constexpr int kInFlight = 8;  // records fetched together (16: config 2 19.6 us but 256 x 4096 79.5; 4: 20.5 / 74.5)
+        for (int u0 = 0; u0 < n_rec; u0 += kInFlight) {
+            float4 v[kInFlight];
+            float w[kInFlight];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < kInFlight; ++i) {
                 const float* rec = record(min(u0 + i, n_rec - 1));
                 v[i] = *reinterpret_cast<const float4*>(rec + hh * D + d);
                 w[i] = rec[kAttnHeads * D + hh];
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < kInFlight; ++i)
                 if (u0 + i < n_rec) { a.x += v[i].x; a.y += v[i].y; a.z += v[i].z; a.w += v[i].w; l += w[i]; }
         }
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
@@ -1130,7 +1142,7 @@ StreamPlan spk_attn_stream_plan(int T, int64_t n_seqs, int Hq, int Hkv, int head
             if (workers < items) workers = items < cap ? items : cap;
             pl.workers = workers;
         }
-        if (pl.cut) range_bytes = ((workers * 2 * rec_bytes + 15) / 16) * 16 + (n_seqs + 1) * static_cast<int64_t>(sizeof(int));
+        if (pl.cut) range_bytes = workers * 2 * rec_bytes;
     }
     // the tcgen05 form (selectable at head_dim 64) uses the unit records
     const bool unit_form_possible = !pl.dense || head_dim == 64;
@@ -1216,9 +1228,6 @@ int spk_attn_stream_launch(const AttnParams& p, const StreamPlan& plan, int head
         const int64_t resident = 148LL * kWarps * stream_ctas_per_sm(head_dim, wide);
         sp.workers = plan.workers < resident ? plan.workers : resident;
         sp.dense_ws = p.ws;
-        sp.prefix_out = plan.cut ? reinterpret_cast<int*>(reinterpret_cast<char*>(p.ws) +
-                                                          ((plan.workers * 2 * plan.rec_floats * 4 + 15) / 16) * 16)
-                                 : nullptr;
         ctas = (sp.workers + kWarps - 1) / kWarps;
         combine = plan.cut;
         if (!plan.cut && sp.workers >= p.n_seqs * sp.gt) {

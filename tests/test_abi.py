@@ -58,7 +58,7 @@ def test_host_side_argument_checks(lib):
     assert lib.spk_attn_decode(*args(48, 16)) == -6
     assert lib.spk_attn_decode(*args(64, 12)) == -6
     assert lib.spk_attn_decode(*args(256, 16)) == -6
-    # workspace of the streaming form: two partial records per worker warp plus the step prefix, and only when a
+    # workspace of the streaming form: two partial records per worker warp, and only when a
     # sequence can be long enough (more than 256 keys) to be cut between warps.  Workers: one per eight 32-key
     # steps of the fully loaded batch, at most 148 SMs x 16 warps.
     record = (8 * 64 + 8) * 4                    # eight heads x 64 sums + 8 totals, fp32
@@ -67,10 +67,10 @@ def test_host_side_argument_checks(lib):
     # tables of up to 768 keys are never cut (one warp walks such a row faster than a combine pass would cost)
     # (what is left at 48 pages are the two 512-key unit records per item of the selectable tcgen05 form)
     assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 48) == 64 * 4 * 2 * 2 * record
-    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 49) == (64 * 4 * 2 * 25 // 8) * 2 * record + 65 * 4
-    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 256) == 148 * 16 * 2 * record + 65 * 4
+    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 49) == (64 * 4 * 2 * 25 // 8) * 2 * record
+    assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 64, 16, 256) == 148 * 16 * 2 * record
     ws = lib.spk_attn_decode_workspace_bytes(4, 8, 14, 2, 64, 16, 256)
-    assert ws == (8 * 4 * 2 * 128 // 8) * 2 * record + 9 * 4
+    assert ws == (8 * 4 * 2 * 128 // 8) * 2 * record
     assert lib.spk_attn_decode_workspace_bytes(4, 64, 14, 2, 48, 16, 256) == 0
     # workspace required but missing -> rejected on the host, nothing launched
     big = (1, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 1, 1, _lib.F32, 0, 0, 0,
