@@ -954,6 +954,10 @@ attn_tc_kernel(const AttnParams p, const StreamParams sp) {
 // Sums the partial records of one (sequence, KV head, pass, timestep) in key order and divides.  Items that one
 // warp finished alone were written by the main kernel and are skipped.  A thread owns four channels of one head;
 // the records' values are fetched eight records at a time (independent loads) and added in record order.
+// MAXW: the most records a thread fetches together.  Sixteen shortens the pass for items of many pieces but costs
+// registers (128 against 80), which the many small CTAs of a large batch pay for in residency; the host picks
+// sixteen for calls of up to 512 items.
+template <int MAXW>
 __global__ void __launch_bounds__(128)
 attn_stream_combine_kernel(const AttnParams p, const StreamParams sp, int D) {
     // a following launch that asked to overlap (it waits for this grid before it touches q, K/V or the records)
@@ -1013,25 +1017,33 @@ attn_stream_combine_kernel(const AttnParams p, const StreamParams sp, int D) {
         return sp.dense ? sp.dense_ws + (2 * (first + u) + (u == 0 ? 1 : 0)) * sp.rec : p.ws + (item * sp.max_units + u) * sp.rec;
     };
     const int quads = D / 4;
-    for (int idx = threadIdx.x; idx < nh * quads; idx += blockDim.x) {
+    // (head, four channels) pairs of the item over the threads of its gridDim.y CTAs: one pair per thread
+    for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < nh * quads; idx += gridDim.y * blockDim.x) {
         const int hh = idx / quads;
         const int d = 4 * (idx - hh * quads);
         float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         float l = 0.0f;
-        constexpr int kInFlight = 8;  // records fetched together (16: config 2 19.6 us but 256 x 4096 79.5; 4: 20.5 / 74.5)
-        for (int u0 = 0; u0 < n_rec; u0 += kInFlight) {
-            float4 v[kInFlight];
-            float w[kInFlight];
+        // records fetched together (independent loads), added in record order; as many in flight as the item has
+        // pieces, up to MAXW (indices past the last piece re-read the last record and are not added)
+        auto add_records = [&](auto width) {
+            constexpr int kInFlight = decltype(width)::value;
+            for (int u0 = 0; u0 < n_rec; u0 += kInFlight) {
+                float4 v[kInFlight];
+                float w[kInFlight];
 #pragma unroll
-            for (int i = 0; i < kInFlight; ++i) {
-                const float* rec = record(min(u0 + i, n_rec - 1));
-                v[i] = *reinterpret_cast<const float4*>(rec + hh * D + d);
-                w[i] = rec[kAttnHeads * D + hh];
+                for (int i = 0; i < kInFlight; ++i) {
+                    const float* rec = record(min(u0 + i, n_rec - 1));
+                    v[i] = *reinterpret_cast<const float4*>(rec + hh * D + d);
+                    w[i] = rec[kAttnHeads * D + hh];
+                }
+#pragma unroll
+                for (int i = 0; i < kInFlight; ++i)
+                    if (u0 + i < n_rec) { a.x += v[i].x; a.y += v[i].y; a.z += v[i].z; a.w += v[i].w; l += w[i]; }
             }
-#pragma unroll
-            for (int i = 0; i < kInFlight; ++i)
-                if (u0 + i < n_rec) { a.x += v[i].x; a.y += v[i].y; a.z += v[i].z; a.w += v[i].w; l += w[i]; }
-        }
+        };
+        if (n_rec <= 4) add_records(std::integral_constant<int, 4>{});
+        else if (MAXW <= 8 || n_rec <= 8) add_records(std::integral_constant<int, 8>{});
+        else add_records(std::integral_constant<int, MAXW>{});
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         const int64_t o = t * p.so_t + row * p.so_n + (h0 + hh) * p.so_h + d;
         const float r4[4] = {a.x * inv, a.y * inv, a.z * inv, a.w * inv};
@@ -1168,7 +1180,7 @@ static int launch_combine(const AttnParams& p, const StreamParams& sp, int head_
     // runs (the launch latency overlaps), and each waits for the main grid before it reads a record.
     if (p.n_seqs * sp.gt > 0x7fffffffLL) return SPK_ERR_TOO_LARGE;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(p.n_seqs * sp.gt));
+    cfg.gridDim = dim3(static_cast<unsigned>(p.n_seqs * sp.gt), static_cast<unsigned>((kAttnHeads * (head_dim / 4) + 127) / 128));
     cfg.blockDim = dim3(128);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
@@ -1177,7 +1189,8 @@ static int launch_combine(const AttnParams& p, const StreamParams& sp, int head_
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, attn_stream_combine_kernel, p, sp, head_dim);
+    const cudaError_t e = p.n_seqs * sp.gt <= 512 ? cudaLaunchKernelEx(&cfg, attn_stream_combine_kernel<16>, p, sp, head_dim)
+                                                   : cudaLaunchKernelEx(&cfg, attn_stream_combine_kernel<8>, p, sp, head_dim);
     if (e != cudaSuccess) return spk_set_cuda_error(e);
     spk_count_launch();
     return SPK_OK;
