@@ -1047,6 +1047,22 @@ attn_stream_combine_kernel(const AttnParams p, const StreamParams sp, int D) {
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         const int64_t o = t * p.so_t + row * p.so_n + (h0 + hh) * p.so_h + d;
         const float r4[4] = {a.x * inv, a.y * inv, a.z * inv, a.w * inv};
+        if (sp.out_vec) {  // rows 16-byte aligned: the four channels leave as one store
+            if (p.out_dtype == SPK_F32) {
+                *reinterpret_cast<float4*>(static_cast<float*>(p.out) + o) = make_float4(r4[0], r4[1], r4[2], r4[3]);
+            } else if (p.out_dtype == SPK_BF16) {
+                union { uint2 u; __nv_bfloat162 h[2]; } pk;
+                pk.h[0] = __floats2bfloat162_rn(r4[0], r4[1]);
+                pk.h[1] = __floats2bfloat162_rn(r4[2], r4[3]);
+                *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.out) + o) = pk.u;
+            } else {
+                union { uint2 u; __half2 h[2]; } pk;
+                pk.h[0] = __floats2half2_rn(r4[0], r4[1]);
+                pk.h[1] = __floats2half2_rn(r4[2], r4[3]);
+                *reinterpret_cast<uint2*>(static_cast<__half*>(p.out) + o) = pk.u;
+            }
+            continue;
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             if (p.out_dtype == SPK_F32) static_cast<float*>(p.out)[o + i] = r4[i];
