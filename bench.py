@@ -539,6 +539,78 @@ def lif_roofline(device, n_tok: int = 8192, iters: int = 10, repeats: int = 5) -
     return out
 
 
+def step_kernels(device, repeats: int = 5, chain: int = 40) -> dict:
+    """This library's kernels at the shapes of one decode layer of the headline workload (64 rows, T = 4, 0.5B
+    shape), each `chain` times back to back inside one CUDA graph on warm operands, next to an empty-ish torch
+    kernel and the four library GEMMs of the layer: what a launch costs when it is launch-latency-sized."""
+    import torch.nn.functional as F
+
+    import cases
+    from spikeinfer_b200 import kernels
+
+    T, n, Hq, Hkv, D, hid, inter = 4, N_REQ, 14, 2, 64, 896, 4864
+    bf = torch.bfloat16
+    g = torch.Generator(device=device).manual_seed(11)
+    rnd = lambda *shape: torch.randn(shape, generator=g, device=device).to(bf)
+
+    def timed(fn) -> dict:
+        fn()
+        torch.cuda.synchronize(device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(chain):
+                fn()
+        for _ in range(3):
+            graph.replay()
+        us = []
+        for _ in range(repeats):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(device)
+            start.record()
+            graph.replay()
+            stop.record()
+            torch.cuda.synchronize(device)
+            us.append(start.elapsed_time(stop) * 1e3 / chain)
+        return stats(us, 2)
+
+    out = {}
+    z = torch.zeros(32, device=device)
+    out["empty_torch_kernel"] = timed(lambda: z.add_(1.0))
+    h, dl, wn = rnd(T * n, hid), rnd(T * n, hid), torch.ones(hid, device=device, dtype=bf)
+    out["add_rms_norm_256x896"] = timed(lambda: kernels.add_rms_norm(h, dl, wn, 1e-6))
+    qkv = rnd(T, n, (Hq + 2 * Hkv) * D)
+    beta, th = torch.full((D,), 0.9, device=device), torch.ones(D, device=device)
+    cos, sin = rnd(n, D), rnd(n, D)
+    slots = torch.randperm(4096, generator=g, device=device)[:n]
+    kc = torch.zeros(T, Hkv, 4096, 2, dtype=torch.int32, device=device)
+    vc = torch.zeros_like(kc)
+    qp = torch.empty(T, n, Hq, 2, dtype=torch.int32, device=device)
+    xq = qkv[..., : Hq * D].unflatten(-1, (Hq, D))
+    xk = qkv[..., Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
+    xv = qkv[..., (Hq + Hkv) * D:].unflatten(-1, (Hkv, D))
+    S = kernels.LifSiteSpec
+    pool = lambda c: dict(packed=c, packed_strides=(c.stride(0), c.stride(2), c.stride(1)), slot_mapping=slots, num_rows=4096)
+    sites = [S(x=xq, beta=beta, threshold=th, packed=qp, packed_strides=(n * Hq * 2, Hq * 2, 2), rope_cos=cos, rope_sin=sin),
+             S(x=xk, beta=beta, threshold=th, rope_cos=cos, rope_sin=sin, **pool(kc)),
+             S(x=xv, beta=beta, threshold=th, **pool(vc))]
+    out["lif_qkv_rope_pack_scatter"] = timed(lambda: kernels.lif_pack_scatter(sites))
+    case = cases.attention_case(seq_lens=[130 + (i % 70) for i in range(n)], density=0.15, seed=2, max_blocks=16)
+    d = {k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in case.items()}
+    ctx = torch.empty(T, n, Hq, D, dtype=bf, device=device)
+    out["attention_64_rows_130_to_199_keys"] = timed(lambda: kernels.paged_spike_attn_decode(**d, out=ctx))
+    gu = rnd(T, n, 2 * inter)
+    gb, gth = torch.full((inter,), 0.9, device=device), torch.ones(inter, device=device)
+    out["lif_gate_times_up"] = timed(lambda: kernels.lif_gate_mul(gu[..., :inter], gu[..., inter:], gb, gth))
+    x = rnd(T * n, hid)
+    for name, N_, K_, bias in (("gemm_qkv", (Hq + 2 * Hkv) * D, hid, True), ("gemm_o", hid, hid, False),
+                               ("gemm_gate_up", 2 * inter, hid, False), ("gemm_down", hid, inter, False)):
+        a = x if K_ == hid else rnd(T * n, K_)
+        w = (rnd(N_, K_).float() * 0.05).to(bf)
+        b = rnd(N_) if bias else None
+        out[name + "_library"] = timed(lambda: F.linear(a, w, b))
+    return {"unit": "us per launch, median/min/max", "chain": chain, "kernels": out}
+
+
 def run_kernel_bench(args) -> None:
     """Kernel-level configurations only (also the small cases the ncu captures under profiles/ run)."""
     device = torch.device("cuda", 0)
@@ -548,7 +620,9 @@ def run_kernel_bench(args) -> None:
 
         form = {"general": _lib.ATTN_FORM_GENERAL, "tcgen05": _lib.ATTN_FORM_TCGEN05}[args.attn_form]
         _lib.check(_lib.load().spk_attn_select_form(form), "spk_attn_select_form")
-    if args.kernel_bench == "attn":
+    if args.kernel_bench == "step":
+        res = step_kernels(device, repeats=args.repeats)
+    elif args.kernel_bench == "attn":
         res = attention_roofline(device, n_pools=args.pools, iters=args.steps, repeats=args.repeats, extra=False,
                                  uniform=(args.rows, args.keys) if args.rows and args.keys else None)
     else:
@@ -941,7 +1015,7 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    ap.add_argument("--kernel-bench", choices=["attn", "lif"], default=None,
+    ap.add_argument("--kernel-bench", choices=["attn", "lif", "step"], default=None,
                     help="time only the kernel-level configuration of the attention or the LIF kernel")
     ap.add_argument("--attn-page-major", action="store_true",
                     help="kernel-level attention timing on the page-major pool layout [block, T, H_kv, K|V, slot, W]")
