@@ -221,7 +221,7 @@ def build_engine(model, prompts: torch.Tensor, max_len: int, device):
     lib = _lib.load()
     before = lib.spk_launch_count()
     engine.capture()
-    launches_per_step = (lib.spk_launch_count() - before) // 4  # three warm-up passes and the captured one
+    launches_per_step = (lib.spk_launch_count() - before) // 5  # three warm-up passes and the two captured forms
     torch.cuda.synchronize(device)
     engine.state.check_status()
     return engine, launches_per_step
@@ -938,7 +938,7 @@ def run_tp7b(args) -> None:
     lib = _lib.load()
     before = lib.spk_launch_count()
     engine.capture()
-    launches_per_step = (lib.spk_launch_count() - before) // 4
+    launches_per_step = (lib.spk_launch_count() - before) // 5  # three warm-up passes and the two captured forms
     torch.cuda.synchronize(device)
     stage("decode graph captured")
 

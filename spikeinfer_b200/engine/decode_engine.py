@@ -43,6 +43,7 @@ class SpikeDecodeEngine:
         # row counts a step can run on: powers of two up to max_num_seqs, and max_num_seqs itself
         self.buckets = row_buckets(max_num_seqs) if graph_buckets else [max_num_seqs]
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.host_graphs: dict[int, torch.cuda.CUDAGraph] = {}
         # True: prompts attend through the packed popcount kernel in one batched launch per layer (3x faster at
         # 64 prompts of 128 tokens, exact-score fp32 softmax).  False (default): one SDPA per sequence on unpacked
         # spikes in the model dtype, as the reference does; in bf16 that rounds the probabilities to bf16, so
@@ -159,6 +160,7 @@ class SpikeDecodeEngine:
         if value is not None:
             raise ValueError("assign None to drop the captured graphs")
         self.graphs.clear()
+        self.host_graphs.clear()
 
     @torch.no_grad()
     def capture(self, rows: int | None = None) -> None:
@@ -182,6 +184,14 @@ class SpikeDecodeEngine:
         with torch.cuda.graph(graph, pool=pool):
             self._body(rows)
         self.graphs[rows] = graph
+        # the host-in-the-loop form of the same step: the token copies from and to pinned host memory are nodes of
+        # the graph (fixed addresses: host_in, host_out), so a step is one launch and one wait on the host side
+        host_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(host_graph, pool=graph.pool()):
+            st.next_tokens[:rows].copy_(self.host_in[:rows], non_blocking=True)
+            self._body(rows)
+            self.host_out[:rows].copy_(st.next_tokens[:rows], non_blocking=True)
+        self.host_graphs[rows] = host_graph
         for t, s in zip(self._state_tensors(), saved):
             t.copy_(s)
         st.active.copy_(active)
@@ -227,9 +237,20 @@ class SpikeDecodeEngine:
     def step_host(self, tokens_in: torch.Tensor | None = None) -> torch.Tensor:
         """Host-in-the-loop step: ``tokens_in`` (pinned int64 ``[max_num_seqs]``, the tokens to feed) is
         copied to the device, the step runs, and the sampled tokens are returned in pinned host memory."""
-        if tokens_in is not None:
-            self.state.next_tokens.copy_(tokens_in, non_blocking=True)
-        self.decode_step()
-        self.host_out.copy_(self.state.next_tokens, non_blocking=True)
+        if not self.use_graph or tokens_in is None:
+            if tokens_in is not None:
+                self.state.next_tokens.copy_(tokens_in, non_blocking=True)
+            self.decode_step()
+            self.host_out.copy_(self.state.next_tokens, non_blocking=True)
+            torch.cuda.current_stream(self.device).synchronize()
+            return self.host_out
+        # one replay holds the copy in, the step and the copy out
+        rows = self.bucket_for_batch()
+        if rows not in self.host_graphs:
+            self.capture(rows)
+        if tokens_in.data_ptr() != self.host_in.data_ptr():
+            self.host_in.copy_(tokens_in)  # host to host: the graph reads the engine's own pinned buffer
+        self.host_graphs[rows].replay()
+        self.ledger.advance()
         torch.cuda.current_stream(self.device).synchronize()
         return self.host_out
