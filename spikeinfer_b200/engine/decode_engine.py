@@ -26,7 +26,7 @@ from .spike_cache import PagedSpikeCache
 class SpikeDecodeEngine:
     def __init__(self, model: SpikingQwenModel, num_blocks: int, block_size: int = 16, max_num_seqs: int = 64,
                  max_model_len: int = 4096, use_graph: bool = True, packed_prefill: bool = False,
-                 graph_buckets: bool = True) -> None:
+                 graph_buckets: bool = True, short_context_keys: int = 768) -> None:
         c = model.config
         self.model = model
         self.device = model.device
@@ -44,6 +44,13 @@ class SpikeDecodeEngine:
         self.buckets = row_buckets(max_num_seqs) if graph_buckets else [max_num_seqs]
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.host_graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        # While no row holds more than `short_context_keys` keys (the host knows: BlockLedger) a step is replayed from
+        # graphs whose attention calls see only that many table entries: up to 768 keys the attention cuts no row,
+        # so those calls have no combine pass, whatever max_model_len is.  0 pages = the tables are that short anyway.
+        short = min(self.max_blocks, max(short_context_keys, 0) // block_size)
+        self.short_blocks = short if 0 < short < self.max_blocks else 0
+        self.short_graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.short_host_graphs: dict[int, torch.cuda.CUDAGraph] = {}
         # True: prompts attend through the packed popcount kernel in one batched launch per layer (3x faster at
         # 64 prompts of 128 tokens, exact-score fp32 softmax).  False (default): one SDPA per sequence on unpacked
         # spikes in the model dtype, as the reference does; in bf16 that rounds the probabilities to bf16, so
@@ -126,23 +133,32 @@ class SpikeDecodeEngine:
         self.free_rows = list(snap["free_rows"])
 
     # -- decode -----------------------------------------------------------
-    def _meta(self, rows: int) -> AttentionMetadata:
+    def _meta(self, rows: int, short: bool = False) -> AttentionMetadata:
         st = self.state
+        tables = st.block_tables[:rows, :self.short_blocks] if short else st.block_tables[:rows]
         # tables and lengths are written by the metadata kernel at the head of the step, layers before any attention
         return AttentionMetadata(
             slot_mapping=st.slot_mapping[:rows], block_size=self.block_size, num_decode_tokens=rows,
-            block_tables=st.block_tables[:rows], seq_lens=st.seq_lens[:rows], status=st.status, tables_settled=True)
+            block_tables=tables, seq_lens=st.seq_lens[:rows], status=st.status, tables_settled=True)
+
+    def short_context(self) -> bool:
+        """True when the step about to run touches no more than the short tables hold in any row."""
+        if not self.short_blocks:
+            return False
+        longest = max(self.ledger.seq_lens.values(), default=0) + 1  # the token being decoded included
+        return longest <= self.short_blocks * self.block_size
 
     @property
     def meta(self) -> AttentionMetadata:
         """Decode metadata over all rows."""
         return self._meta(self.max_num_seqs)
 
-    def _body(self, rows: int | None = None) -> None:
+    def _body(self, rows: int | None = None, short: bool = False) -> None:
         st = self.state
         rows = self.max_num_seqs if rows is None else rows
         st.advance(rows)
-        hidden = self.model.forward_paged(st.input_ids[:rows], st.positions[:rows], self.cache.layers, self._meta(rows))
+        hidden = self.model.forward_paged(st.input_ids[:rows], st.positions[:rows], self.cache.layers,
+                                          self._meta(rows, short))
         logits = self.model.compute_logits(hidden)
         argmax_rows(logits, out=st.next_tokens[:rows], workspace=self.sample_ws)  # greedy, inside the graph
 
@@ -161,13 +177,16 @@ class SpikeDecodeEngine:
             raise ValueError("assign None to drop the captured graphs")
         self.graphs.clear()
         self.host_graphs.clear()
+        self.short_graphs.clear()
+        self.short_host_graphs.clear()
 
     @torch.no_grad()
-    def capture(self, rows: int | None = None) -> None:
-        """Capture one decode step over ``rows`` rows (default: all).  Warm-up runs would advance real rows, so
-        capture happens on a snapshot of the batch state and the pools' pad block only: the state is saved and
-        restored.  All buckets share one memory pool (they never run at the same time)."""
+    def capture(self, rows: int | None = None, short: bool = False) -> None:
+        """Capture one decode step over ``rows`` rows (default: all), with full or short tables.  Warm-up runs would
+        advance real rows, so capture happens on a snapshot of the batch state and the pools' pad block only: the
+        state is saved and restored.  All graphs share one memory pool (they never run at the same time)."""
         rows = self.max_num_seqs if rows is None else rows
+        graphs, host_graphs = (self.short_graphs, self.short_host_graphs) if short else (self.graphs, self.host_graphs)
         st = self.state
         saved = [t.clone() for t in self._state_tensors()]
         active = st.active.clone()
@@ -176,22 +195,22 @@ class SpikeDecodeEngine:
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
             for _ in range(3):
-                self._body(rows)
+                self._body(rows, short)
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
-        pool = next(iter(self.graphs.values())).pool() if self.graphs else None
-        with torch.cuda.graph(graph, pool=pool):
-            self._body(rows)
-        self.graphs[rows] = graph
+        any_graph = next(iter(self.graphs.values()), None) or next(iter(self.short_graphs.values()), None)
+        with torch.cuda.graph(graph, pool=any_graph.pool() if any_graph is not None else None):
+            self._body(rows, short)
+        graphs[rows] = graph
         # the host-in-the-loop form of the same step: the token copies from and to pinned host memory are nodes of
         # the graph (fixed addresses: host_in, host_out), so a step is one launch and one wait on the host side
         host_graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(host_graph, pool=graph.pool()):
             st.next_tokens[:rows].copy_(self.host_in[:rows], non_blocking=True)
-            self._body(rows)
+            self._body(rows, short)
             self.host_out[:rows].copy_(st.next_tokens[:rows], non_blocking=True)
-        self.host_graphs[rows] = host_graph
+        host_graphs[rows] = host_graph
         for t, s in zip(self._state_tensors(), saved):
             t.copy_(s)
         st.active.copy_(active)
@@ -201,17 +220,21 @@ class SpikeDecodeEngine:
         for b in sorted(self.buckets, reverse=True):
             if b not in self.graphs:
                 self.capture(b)
+            if self.short_blocks and b not in self.short_graphs:
+                self.capture(b, short=True)
 
     @torch.no_grad()
     def decode_step(self) -> None:
         """One token for every active row; tokens stay on the device (``state.next_tokens``)."""
         rows = self.bucket_for_batch()
+        short = self.short_context()
         if self.use_graph:
-            if rows not in self.graphs:
-                self.capture(rows)
-            self.graphs[rows].replay()
+            graphs = self.short_graphs if short else self.graphs
+            if rows not in graphs:
+                self.capture(rows, short)
+            graphs[rows].replay()
         else:
-            self._body(rows)
+            self._body(rows, short)
         self.ledger.advance()
 
     @torch.no_grad()
@@ -246,11 +269,13 @@ class SpikeDecodeEngine:
             return self.host_out
         # one replay holds the copy in, the step and the copy out
         rows = self.bucket_for_batch()
-        if rows not in self.host_graphs:
-            self.capture(rows)
+        short = self.short_context()
+        host_graphs = self.short_host_graphs if short else self.host_graphs
+        if rows not in host_graphs:
+            self.capture(rows, short)
         if tokens_in.data_ptr() != self.host_in.data_ptr():
             self.host_in.copy_(tokens_in)  # host to host: the graph reads the engine's own pinned buffer
-        self.host_graphs[rows].replay()
+        host_graphs[rows].replay()
         self.ledger.advance()
         torch.cuda.current_stream(self.device).synchronize()
         return self.host_out

@@ -223,6 +223,35 @@ def test_bucket_graphs_follow_the_batch(dev, golden):
     assert logs[0] == logs[1]
 
 
+def test_short_context_graphs_hand_over_to_the_full_tables(dev, golden):
+    """With tables far wider than the contexts in flight (max_model_len 2048 here), steps run from graphs whose
+    attention sees only the first few table entries for as long as the host's ledger says every row fits them, then
+    from the full-table graphs; the tokens equal those of an engine that always uses the full tables."""
+    g, shape, w = build(golden, "random_lif")
+    model = SpikingQwenModel(SpikingQwenConfig(**g["config"]), w, device=dev)
+    prompts = tiny_prompts(shape.vocab_size)
+    logs = []
+    for keys in (48, 0):
+        eng = SpikeDecodeEngine(model, g["num_blocks"], g["block_size"], max_num_seqs=4, max_model_len=2048,
+                                short_context_keys=keys)
+        assert eng.short_blocks == (3 if keys else 0)
+        eng.add_requests(prompts)
+        log, used_short = [], []
+        for _ in range(22):
+            used_short.append(eng.short_context())
+            eng.decode_step()
+            log.append(eng.state.next_tokens[:4].tolist())
+        eng.state.check_status()
+        if keys:
+            # prompts of 32 tokens: the step that decodes token 33..48 fits three pages of 16, the next ones do not
+            assert used_short == [True] * 16 + [False] * 6
+            assert sorted(eng.short_graphs) == [4] and sorted(eng.graphs) == [4]
+        else:
+            assert not any(used_short) and not eng.short_graphs
+        logs.append(log)
+    assert logs[0] == logs[1]
+
+
 def test_admission_control_and_block_ledger(dev, golden):
     """Over-admission raises before anything is taken from the device list and leaves pools, tables and the free
     list untouched; the host ledger's free count equals the device's after prefill, decode steps and a release."""
